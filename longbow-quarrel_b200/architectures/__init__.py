@@ -1,1 +1,1 @@
-from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import fetorax, llama  # noqa: F401  (registers LlamaForCausalLM and Fetorax)

@@ -21,17 +21,19 @@ NO_PAGE = -1
 
 class PagedKVGroup(CacheGroup):
     def __init__(self, entries: list[int], n_kv_heads: int, head_dim: int, window: int | None, n_pages: int,
-                 page_size: int, max_slots: int, max_pages_per_seq: int, dtype: torch.dtype, device):
+                 page_size: int, max_slots: int, max_pages_per_seq: int, dtype: torch.dtype, device,
+                 v_head_dim: int | None = None):
         self.entries = list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.n_kv_heads, self.head_dim, self.window = n_kv_heads, head_dim, window
+        self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
         self.page_size, self.n_pages, self.max_pages_per_seq = page_size, n_pages, max_pages_per_seq
         shape = (len(self.entries), n_pages, n_kv_heads, page_size, head_dim)
         # Kernels that load whole pages multiply the rows beyond a sequence's length by probability zero,
         # which needs finite values there: the pool starts zero-filled, and a page that is handed out
         # again has the rows that its new owner's step does not write cleared first (`_to_clear`).
         self.k_pages = torch.zeros(shape, dtype=dtype, device=device)
-        self.v_pages = torch.zeros(shape, dtype=dtype, device=device)
+        self.v_pages = torch.zeros((*shape[:4], self.v_head_dim), dtype=dtype, device=device)
         self.table = np.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=np.int32)
         self.table_dev = torch.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=torch.int32, device=device)
         self._free = list(range(n_pages - 1, -1, -1))
@@ -152,7 +154,7 @@ class PagedKVGroup(CacheGroup):
         return KVView(self, entry)
 
     def nbytes(self) -> int:
-        return 2 * self.k_pages.numel() * self.k_pages.element_size()
+        return (self.k_pages.numel() + self.v_pages.numel()) * self.k_pages.element_size()
 
     def pages_in_use(self) -> int:
         return self.n_pages - len(self._free)
@@ -168,4 +170,4 @@ class KVView:
         self.page_table = group.table_dev
         self.page_size = group.page_size
         self.window = group.window
-        self.n_kv_heads, self.head_dim = group.n_kv_heads, group.head_dim
+        self.n_kv_heads, self.head_dim, self.v_head_dim = group.n_kv_heads, group.head_dim, group.v_head_dim

@@ -32,9 +32,12 @@ def registered_architectures() -> list[str]:
 
 
 def architecture_of(data: dict) -> Architecture:
+    """By `architectures` (a list whose first entry names the model class) or `architecture` (the name itself)."""
     archs = data.get("architectures")
+    if archs is None and isinstance(data.get("architecture"), str):
+        archs = [data["architecture"]]
     if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list that names the model class")
+        raise ConfigError("config.json: 'architectures' (a list) or 'architecture' (a string) must name the model class")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"config.json: architecture {name!r} is not registered "

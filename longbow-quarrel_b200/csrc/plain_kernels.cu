@@ -135,6 +135,65 @@ LQ_EXPORT int lq_rmsnorm(const float* x, const float* gain, const int* rows, voi
                : launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps);
 }
 
+// ------------------------------------------------------------------ norm of a branch, added to the stream
+// x += y / rms(y) * gain for rows of a branch's output y [T, D] (float32): the stream takes the branch after
+// the branch's own norm.  With next_gain, the rows of the norm that reads the stream next are made on the way:
+// h = x / rms(x) * next_gain, in the activation dtype.  Sums run in an order fixed by D alone.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x,
+                   const float* __restrict__ next_gain, TO* __restrict__ h, int D, float eps, float next_eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float partial[8];
+    __shared__ float scale_s;
+    const int r = blockIdx.x;
+    const float* yr = y + (size_t)r * D;
+    float* xr = x + (size_t)r * D;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += 256) s = fmaf(yr[i], yr[i], s);
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        scale_s = 1.0f / sqrtf(t / (float)D + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    s = 0.f;
+    for (int i = threadIdx.x; i < D; i += 256) {
+        const float v = xr[i] + yr[i] * scale * gain[i];
+        xr[i] = v;
+        s = fmaf(v, v, s);
+    }
+    if (!next_gain) return;
+    s = warp_sum(s);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        scale_s = 1.0f / sqrtf(t / (float)D + next_eps);
+    }
+    __syncthreads();
+    const float scale2 = scale_s;
+    for (int i = threadIdx.x; i < D; i += 256) h[(size_t)r * D + i] = from_f32<TO>(xr[i] * scale2 * next_gain[i]);
+}
+
+LQ_EXPORT int lq_rmsnorm_add(const float* y, const float* gain, float* x, const float* next_gain, void* h, int h_dtype,
+                             int n_rows, int D, float eps, float next_eps, cudaStream_t stream) {
+    if (n_rows <= 0) return LQ_OK;
+    if (h_dtype == LQ_F32)
+        return launch_pdl(rmsnorm_add_kernel<float>, dim3(n_rows), dim3(256), 0, stream, y, gain, x, next_gain, (float*)h, D, eps, next_eps);
+    if (h_dtype == LQ_BF16)
+        return launch_pdl(rmsnorm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, y, gain, x, next_gain,
+                          (__nv_bfloat16*)h, D, eps, next_eps);
+    return LQ_BAD_DTYPE;
+}
+
 // ------------------------------------------------------------------ linear (FFMA)
 // C[M,N] = A[M,K] . W[N,K]^T (+ residual[M,N]).  Each output is one chain of fused
 // multiply-adds over k = 0..K-1 in rising order, whatever M is.
@@ -364,6 +423,122 @@ LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const f
     return LQ_BAD_DTYPE;
 }
 
+// ------------------------------------------------------------------ biases, partial rotation, cache write
+// Rows of `buf` [T, stride] hold n_rot heads of size hd side by side from column 0 (queries, then keys where
+// the layer has keys of its own), and from column v_off Hkv value heads of size vd.  Each of the n_rot heads
+// gets its bias (bias[column], optional) and has its first `rot` dimensions rotated in pairs (i, i + rot/2)
+// by the angle of its row's position (cos/sin tables [positions, rot/2]); the rest of the head passes.  The
+// result is written back in place.  With a cache, heads k_first.. are also stored into the row's page of
+// k_pages [page][Hkv][page_size][hd], and the values (with their bias) into v_pages [..][vd].
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_partial_kernel(T* __restrict__ buf, int stride, const float* __restrict__ bias, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int rot, const int* __restrict__ tok_pos,
+                    const int* __restrict__ tok_seq, const int* __restrict__ slots, const int* __restrict__ page_table,
+                    int pt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_rot, int k_first, int Hkv,
+                    int hd, int vd, int v_off, int page_size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
+    T* row = buf + (size_t)t * stride;
+    const float* cs = rot ? cos_t + (size_t)pos * half : nullptr;
+    const float* sn = rot ? sin_t + (size_t)pos * half : nullptr;
+    size_t at = 0;
+    if (k_pages) {
+        const int page = page_table[(size_t)slots[tok_seq[t]] * pt_stride + pos / page_size];
+        at = (size_t)page * Hkv * page_size + (pos % page_size);
+    }
+    const int per_head = hd - half;                 // a rotated pair is one piece of work, every other dimension one
+    for (int i = threadIdx.x; i < n_rot * per_head; i += 256) {
+        const int head = i / per_head, j = i % per_head;
+        T* p = row + (size_t)head * hd;
+        const float* b = bias ? bias + (size_t)head * hd : nullptr;
+        T* kd = (k_pages && head >= k_first) ? k_pages + (at + (size_t)(head - k_first) * page_size) * hd : nullptr;
+        if (j < half) {
+            const float u = to_f32(p[j]) + (b ? b[j] : 0.f), w = to_f32(p[j + half]) + (b ? b[j + half] : 0.f);
+            const float c = cs[j], s = sn[j];
+            const T o0 = from_f32<T>(u * c - w * s), o1 = from_f32<T>(w * c + u * s);
+            p[j] = o0;
+            p[j + half] = o1;
+            if (kd) { kd[j] = o0; kd[j + half] = o1; }
+        } else {
+            const int d = j + half;
+            const T o = from_f32<T>(to_f32(p[d]) + (b ? b[d] : 0.f));
+            p[d] = o;
+            if (kd) kd[d] = o;
+        }
+    }
+    if (v_pages) {
+        const T* vsrc = row + v_off;
+        const float* b = bias ? bias + v_off : nullptr;
+        for (int i = threadIdx.x; i < Hkv * vd; i += 256) {
+            const int head = i / vd, j = i % vd;
+            v_pages[(at + (size_t)head * page_size) * vd + j] = from_f32<T>(to_f32(vsrc[i]) + (b ? b[i] : 0.f));
+        }
+    }
+}
+
+LQ_EXPORT int lq_rope_partial(void* buf, int dtype, int stride, const float* bias, const float* cos_t, const float* sin_t,
+                              int rot, const int* tok_pos, const int* tok_seq, const int* slots, const int* page_table,
+                              int pt_stride, void* k_pages, void* v_pages, int T, int n_rot, int k_first, int Hkv, int hd,
+                              int vd, int v_off, int page_size, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (rot % 2 || rot > hd || (rot && (!cos_t || !sin_t)) || (!k_pages) != (!v_pages)) return LQ_BAD_SIZE;
+    if (dtype == LQ_F32)
+        return launch_pdl(rope_partial_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)buf, stride, bias, cos_t, sin_t,
+                          rot, tok_pos, tok_seq, slots, page_table, pt_stride, (float*)k_pages, (float*)v_pages, n_rot,
+                          k_first, Hkv, hd, vd, v_off, page_size);
+    if (dtype == LQ_BF16)
+        return launch_pdl(rope_partial_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)buf, stride, bias,
+                          cos_t, sin_t, rot, tok_pos, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_pages,
+                          (__nv_bfloat16*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size);
+    return LQ_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ activations, soft cap
+// out = act(x), element by element, in float32: 0 relu(x)^2, 1 gelu (tanh form), 2 silu, 3 relu.
+__device__ __forceinline__ float activation(float v, int act) {
+    switch (act) {
+        case 0: { float r = fmaxf(v, 0.f); return r * r; }
+        case 1: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        case 2: return v / (1.f + expf(-v));
+        default: return fmaxf(v, 0.f);
+    }
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, size_t total, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = from_f32<T>(activation(to_f32(x[i]), act));
+}
+
+LQ_EXPORT int lq_activation(const void* x, void* out, int dtype, long long total, int act, cudaStream_t stream) {
+    if (total <= 0) return LQ_OK;
+    if (act < 0 || act > 3) return LQ_BAD_SIZE;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == LQ_F32)
+        return launch_pdl(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)total, act);
+    if (dtype == LQ_BF16)
+        return launch_pdl(activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+                          (__nv_bfloat16*)out, (size_t)total, act);
+    return LQ_BAD_DTYPE;
+}
+
+// x <- cap * tanh(x / cap) in place (float32 logits).
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
+LQ_EXPORT int lq_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return LQ_OK;
+    return launch_pdl(softcap_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, (size_t)total, cap);
+}
+
 // ------------------------------------------------------------------ attention over the cache
 // One block per (token, query head).  Keys start..pos of the token's own sequence are
 // read from its pages in chunks of ATT_CHUNK; the running maximum, sum and output
@@ -378,7 +553,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
                        const T* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ slots, T* __restrict__ out, int H, int Hkv, int hd,
-                       int page_size, float scale, int window) {
+                       int page_size, float scale, int window, int vd, const float* __restrict__ sink,
+                       const T* __restrict__ gate, int gate_stride) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float sm[];
@@ -421,11 +597,11 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
         l = l * corr + ls;
         for (int rep = 0; rep < 2; ++rep) {
             int d = tid + rep * ATT_CHUNK;
-            if (d >= hd) break;
+            if (d >= vd) break;
             float a = 0.f;
             for (int j = 0; j < n; ++j) {
                 int key = base + j;
-                const T* vr = v_pages + (((size_t)pg[j] * Hkv + kvh) * page_size + key % page_size) * hd;
+                const T* vr = v_pages + (((size_t)pg[j] * Hkv + kvh) * page_size + key % page_size) * vd;
                 a = fmaf(sc[j], to_f32(vr[d]), a);
             }
             if (rep == 0) acc0 = acc0 * corr + a; else acc1 = acc1 * corr + a;
@@ -433,26 +609,43 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
         m = cm;
         __syncthreads();
     }
-    T* orow = out + ((size_t)t * H + h) * hd;
-    if (tid < hd) orow[tid] = from_f32<T>(acc0 / l);
-    if (tid + ATT_CHUNK < hd) orow[tid + ATT_CHUNK] = from_f32<T>(acc1 / l);
+    if (sink) {
+        // One more term in the denominator: exp(sink) of the head, with no key and no value.
+        float s = sink[h], cm = fmaxf(m, s), corr = expf(m - cm);
+        l = l * corr + expf(s - cm);
+        acc0 *= corr;
+        acc1 *= corr;
+    }
+    float o0 = acc0 / l, o1 = acc1 / l;
+    if (gate) {
+        // The output gate: each value times sigmoid of the gate's value at the same place.
+        const T* g = gate + (size_t)t * gate_stride + (size_t)h * vd;
+        if (tid < vd) o0 *= 1.f / (1.f + expf(-to_f32(g[tid])));
+        if (tid + ATT_CHUNK < vd) o1 *= 1.f / (1.f + expf(-to_f32(g[tid + ATT_CHUNK])));
+    }
+    T* orow = out + ((size_t)t * H + h) * vd;
+    if (tid < vd) orow[tid] = from_f32<T>(o0);
+    if (tid + ATT_CHUNK < vd) orow[tid + ATT_CHUNK] = from_f32<T>(o1);
 }
 
 LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const void* k_pages, const void* v_pages,
                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                  const int* slots, void* out, int T, int H, int Hkv, int hd, int page_size,
-                                 float scale, int window, cudaStream_t stream) {
+                                 float scale, int window, int vd, const float* sink, const void* gate, int gate_stride,
+                                 cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
-    if (hd > 2 * ATT_CHUNK || H % Hkv) return LQ_BAD_SIZE;
+    if (vd <= 0) vd = hd;
+    if (vd > 2 * ATT_CHUNK || H % Hkv) return LQ_BAD_SIZE;
     dim3 grid(T, H);
     size_t smem = (hd + 2 * ATT_CHUNK) * sizeof(float);
     if (dtype == LQ_F32)
         return launch_pdl(attention_plain_kernel<float>, grid, dim3(ATT_CHUNK), smem, stream, (const float*)q, q_stride, (const float*)k_pages,
-            (const float*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, (float*)out, H, Hkv, hd, page_size, scale, window);
+            (const float*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, (float*)out, H, Hkv, hd, page_size, scale, window,
+            vd, sink, (const float*)gate, gate_stride);
     else if (dtype == LQ_BF16)
         return launch_pdl(attention_plain_kernel<__nv_bfloat16>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window);
+            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const __nv_bfloat16*)gate, gate_stride);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();

@@ -56,9 +56,9 @@ class Engine:
         max_tokens = max_tokens or max_context
         max_context = min(max_context, -(-max_tokens // 64) * 64)
         runtime = Runtime(device=device, dtype=dtype, max_context=max_context)
-        ops.prepare(dtype)
         with torch.cuda.device(device):
             model = Model(spec, runtime)
+            ops.prepare(dtype, extra=model.kernel_libraries())
             tensors = tensors_fn(model.weight_table(), device)
             model.load(tensors)
             del tensors

@@ -81,6 +81,14 @@ class Model:
             out.update(part.step_needs())
         return out
 
+    def kernel_libraries(self) -> tuple:
+        """Kernel libraries that parts of this model name beyond the ones every model uses (built before the first step)."""
+        found = set()
+        for _, part in self._named_parts():
+            for p in (part, *(part.parts() if hasattr(part, "parts") else ())):
+                found.update(getattr(p, "kernel_libraries", ()))
+        return tuple(sorted(found))
+
     def weight_bytes(self) -> int:
         seen, total = set(), 0
         for _, part in self._named_parts():

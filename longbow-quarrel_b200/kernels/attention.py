@@ -146,9 +146,14 @@ def _blocks(ctx, name):
     return tuple(flat.view(4, -1))
 
 
-def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None):
-    """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*hd].  next_w: the weights the
-    stream reads after the attention (the decode kernel asks for their first bytes as it ends)."""
+def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None, vd=None, sink=None, gate=None):
+    """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*vd].  next_w: the weights the
+    stream reads after the attention (the decode kernel asks for their first bytes as it ends).
+    vd: size of a value head (default hd); sink: float32 [H], one more term of each head's softmax
+    denominator; gate: [T, H*vd] whose sigmoid multiplies the output."""
+    vd = vd or hd
+    if vd != hd or sink is not None or gate is not None:
+        return general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate)
     aligned = qkv.stride(0) % 8 == 0
     if not ctx.decode and aligned:
         kind = prefill_kernel(qkv.dtype, hd, cache_view.page_size)
@@ -177,3 +182,10 @@ def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None):
                                next_w=next_w, early_loads=True)      # a decode step: one new token per sequence
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window)
+
+
+def general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate):
+    """Attention with a sink, a gate or values of another size than the keys."""
+    return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
+                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, vd=vd,
+                               sink=sink, gate=gate)

@@ -115,3 +115,9 @@ def linear_swiglu(a: torch.Tensor, weight: LinearWeight, block: int) -> torch.Te
             return out
     gu = linear(a, weight, a.dtype)
     return ops.swiglu(gu, block)
+
+
+def linear_act(a: torch.Tensor, weight: LinearWeight, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(a . W^T), the activation applied in float32 to the product's rounded output, in place."""
+    y = linear(a, weight, out_dtype)
+    return ops.activation(y, activation, out=y)

@@ -136,10 +136,11 @@ def _contig(t: torch.Tensor, what: str) -> torch.Tensor:
     return t
 
 
-def prepare(dtype: torch.dtype, verbose: bool = True) -> None:
-    """Build and load the libraries a model of this dtype uses, before the first step."""
+def prepare(dtype: torch.dtype, verbose: bool = True, extra: tuple = ()) -> None:
+    """Build and load the libraries a model of this dtype uses, before the first step.  extra: libraries
+    that parts of the model name beyond the common ones (`Part.kernel_libraries`)."""
     from concurrent.futures import ThreadPoolExecutor
-    names = ["plain_kernels"] + (["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc"]
+    names = ["plain_kernels", *extra] + (["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc"]
                                              if dtype == torch.bfloat16 else [])
     with ThreadPoolExecutor(max_workers=len(names)) as pool:
         list(pool.map(build.build, names))
@@ -232,20 +233,28 @@ def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor
 
 def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int,
                     hd: int, page_size: int, scale: float, window: int | None,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, vd: int | None = None, sink: torch.Tensor | None = None,
+                    gate: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every token over its own sequence's cache; q is the left
-    H*hd columns of a [T, q_stride] buffer."""
+    H*hd columns of a [T, q_stride] buffer.  vd: size of a value head (default hd).  sink: float32 [H], one
+    more term exp(sink) in each head's softmax denominator.  gate: a [T, H*vd] view (rows may be strided) whose
+    sigmoid multiplies the output."""
     T = q.shape[0]
-    if hd > 256:
-        raise KernelError(f"attention: head_dim {hd} exceeds 256")
+    vd = vd or hd
+    if hd > 256 or vd > 256:
+        raise KernelError(f"attention: head sizes {hd}, {vd} exceed 256")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != H):
+        raise KernelError("attention: sink must be float32 [H]")
+    if gate is not None and (gate.dtype != q.dtype or gate.shape != (T, H * vd) or gate.stride(1) != 1):
+        raise KernelError("attention: the gate must be [T, H * vd] of the queries' dtype with unit column stride")
     if out is None:
-        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, H * vd), dtype=q.dtype, device=q.device)
     fn = _fn("plain_kernels", "lq_attention_plain", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                     c_int, c_float, c_int, c_void_p])
+                                                     c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(fn(_p(q), q.stride(0), dtype_code(q), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0),
               _p(tok_pos), _p(tok_seq), _p(slots), _p(out), T, H, Hkv, hd, page_size, float(scale),
-              int(window or 0), _stream()), "attention")
+              int(window or 0), vd, _p(sink), _p(gate), gate.stride(0) if gate is not None else 0, _stream()), "attention")
     return out
 
 
@@ -265,9 +274,16 @@ def clear_page_tails(k_pages: torch.Tensor, v_pages: torch.Tensor, items: list[t
     """Zero the rows [first, page_size) of the pages in `items` = [(page, first)], in every entry and kv
     head of the pools k_pages, v_pages [entries, pages, kv heads, page_size, head_dim]."""
     from ctypes import c_int as _int
+    if v_pages.shape != k_pages.shape:
+        # Values of another size than the keys: each pool on its own.
+        if v_pages.shape[:4] != k_pages.shape[:4] or v_pages.dtype != k_pages.dtype:
+            raise KernelError("clear_page_tails: keys and values must agree in all but the head size")
+        clear_page_tails(k_pages, k_pages, items)
+        clear_page_tails(v_pages, v_pages, items)
+        return
     E, P, Hkv, page_size, hd = k_pages.shape
-    if v_pages.shape != k_pages.shape or v_pages.dtype != k_pages.dtype:
-        raise KernelError("clear_page_tails: keys and values must have one shape and dtype")
+    if v_pages.dtype != k_pages.dtype:
+        raise KernelError("clear_page_tails: keys and values must have one dtype")
     n = len(items)
     pages = (_int * n)(*[int(p) for p, _ in items])
     first = (_int * n)(*[int(f) for _, f in items])
@@ -276,6 +292,137 @@ def clear_page_tails(k_pages: torch.Tensor, v_pages: torch.Tensor, items: list[t
                                                       c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_p(_contig(k_pages, "k_pages")), _p(_contig(v_pages, "v_pages")), dtype_code(k_pages), pages, first, n,
               E, P, Hkv, page_size, hd, _stream()), "clear_page_tails", -(-n // 120))
+
+
+def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, eps: float, x: torch.Tensor, next_norm: tuple | None = None,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """x += y / rms(y) * gain, row by row, in place (x, y float32 [T, D]): a branch joins the stream after
+    its own norm.  next_norm = (gain, eps) of the norm that reads the stream next: its rows
+    x / rms(x) * gain are made by the same kernel and returned in out_dtype."""
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or gain.dtype != torch.float32 or x.shape != y.shape:
+        raise KernelError("rmsnorm_add reads float32 rows of one shape and float32 gains")
+    T, D = x.shape
+    h = next_gain = None
+    next_eps = 0.0
+    if next_norm is not None:
+        next_gain, next_eps = next_norm
+        if next_gain.dtype != torch.float32 or next_gain.numel() != D:
+            raise KernelError("rmsnorm_add: the next norm's gain must be float32 [D]")
+        h = torch.empty((T, D), dtype=out_dtype, device=x.device)
+    fn = _fn("plain_kernels", "lq_rmsnorm_add", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                 c_float, c_float, c_void_p])
+    _check(fn(_p(_contig(y, "y")), _p(gain), _p(_contig(x, "x")), _p(next_gain), _p(h),
+              dtype_code(out_dtype) if h is not None else F32, T, D, float(eps), float(next_eps), _stream()), "rmsnorm_add")
+    return h
+
+
+def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: int, tok_pos, tok_seq, slots,
+                 page_table, k_pages, v_pages, n_rot: int, k_first: int, Hkv: int, hd: int, vd: int, v_off: int,
+                 page_size: int) -> None:
+    """Biases, rotation of the first `rot` dimensions of each of the n_rot heads at the left of buf's rows (in
+    place), and, with a cache, the store of heads k_first.. into k_pages and of the values at column v_off into
+    v_pages.  bias: float32 over buf's columns, or None; cos/sin: float32 [positions, rot / 2]."""
+    T = buf.shape[0]
+    if buf.stride(1) != 1:
+        raise KernelError("rope_partial: rows must be contiguous")
+    if rot:
+        for t in (cos, sin):
+            if t is None or t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != rot // 2 or not t.is_contiguous():
+                raise KernelError(f"rope_partial: cos/sin tables must be contiguous float32 [positions, {rot // 2}]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() < (v_off + Hkv * vd if k_pages is not None else n_rot * hd)):
+        raise KernelError("rope_partial: the bias must be float32 over the rows' columns")
+    if k_pages is not None and (k_pages.dtype != buf.dtype or v_pages.dtype != buf.dtype):
+        raise KernelError("rope_partial: the cache and the activations must have one dtype")
+    fn = _fn("plain_kernels", "lq_rope_partial", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(buf), dtype_code(buf), buf.stride(0), _p(bias), _p(cos), _p(sin), int(rot), _p(tok_pos), _p(tok_seq),
+              _p(slots), _p(page_table), page_table.stride(0) if page_table is not None else 0, _p(k_pages), _p(v_pages),
+              T, n_rot, k_first, Hkv, hd, vd, v_off, page_size, _stream()), "rope_partial")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def activation(x: torch.Tensor, kind: str, out: torch.Tensor | None = None) -> torch.Tensor:
+    """act(x) element by element, computed in float32: relu2 (the square of relu), gelu_tanh, silu, relu."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} is not one of {', '.join(ACTIVATIONS)}")
+    if out is None:
+        out = torch.empty_like(x)
+    fn = _fn("plain_kernels", "lq_activation", [c_void_p, c_void_p, c_int, c_long, c_int, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(out), dtype_code(x), x.numel(), ACTIVATIONS[kind], _stream()), "activation")
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    if x.dtype != torch.float32:
+        raise KernelError("softcap works on float32 logits")
+    fn = _fn("plain_kernels", "lq_softcap", [c_void_p, c_long, c_float, c_void_p])
+    _check(fn(_p(_contig(x, "x")), x.numel(), float(cap), _stream()), "softcap")
+    return x
+
+
+# ------------------------------------------------------------------ mixers with a matrix state per head
+def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, cu_rows, slots, tok_pos,
+                B: int, H: int, dk: int, dv: int, q_scale: float = 1.0, k_scale: float = 1.0,
+                decay: torch.Tensor | None = None, gates: tuple | None = None, rot: tuple | None = None):
+    """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t for the rows of B sequences (rows cu_rows[b] ..
+    cu_rows[b+1] of qkv belong to the sequence in slot slots[b]), from and into `state` (float32
+    [slots, H, dk (+1), dv (+1)]).  decay: float32 [H] (a_t fixed, b_t = 1).  gates = (pre [rows, 2H] float32,
+    bias [2H] float32, cap): exponential input gate and sigmoid forget gate with a running maximum; the state then
+    has one more row (the maximum) and one more column (the normaliser).  rot = (cos, sin, dims): q and k are
+    rotated as they are read.  Returns the raw outputs float32 [rows, H, dv (+1)] and, with gates,
+    exp(-maximum) float32 [rows, H]."""
+    rows = qkv.shape[0]
+    mlstm = gates is not None
+    dvx, dkx = dv + int(mlstm), dk + int(mlstm)
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, dkx, dvx) or not state.is_contiguous():
+        raise KernelError(f"linear_scan: the state must be contiguous float32 [slots, {H}, {dkx}, {dvx}]")
+    if qkv.stride(1) != 1:
+        raise KernelError("linear_scan: rows must be contiguous")
+    if (decay is None) == (gates is None):
+        raise KernelError("linear_scan takes either a fixed decay or gates")
+    if dk > 256:
+        raise KernelError(f"linear_scan: key size {dk} exceeds 256")
+    out = torch.empty((rows, H, dvx), dtype=torch.float32, device=qkv.device)
+    enm = torch.empty((rows, H), dtype=torch.float32, device=qkv.device) if mlstm else None
+    pre, bias, cap = gates if mlstm else (None, None, 0.0)
+    if mlstm and (pre.dtype != torch.float32 or tuple(pre.shape) != (rows, 2 * H) or not pre.is_contiguous()
+                  or bias.dtype != torch.float32 or bias.numel() != 2 * H):
+        raise KernelError("linear_scan: gates are float32 [rows, 2H] with a float32 bias [2H]")
+    if decay is not None and (decay.dtype != torch.float32 or decay.numel() != H):
+        raise KernelError("linear_scan: decay must be float32 [H]")
+    cos, sin, dims = rot if rot is not None else (None, None, 0)
+    fn = _fn("recurrent", "lq_linear_scan", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_float, c_void_p,
+                                             c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             c_int, c_void_p])
+    _check(fn(_p(qkv), dtype_code(qkv), qkv.stride(0), q_off, k_off, v_off, _p(cos), _p(sin), int(dims), _p(tok_pos),
+              _p(pre), _p(bias), float(cap), _p(decay), float(q_scale), float(k_scale), _p(state), state.stride(0),
+              _p(cu_rows), _p(slots), _p(out), _p(enm), B, H, dk, dv, int(mlstm), _stream()), "linear_scan")
+    return out, enm
+
+
+GATES = {None: 0, "sigmoid": 1, "silu": 2}
+
+
+def head_norm_gate(raw: torch.Tensor, dv: int, eps: float, out_dtype: torch.dtype, exp_neg_m: torch.Tensor | None = None,
+                   weight: torch.Tensor | None = None, gate: torch.Tensor | None = None, act: str | None = None) -> torch.Tensor:
+    """raw float32 [rows, H, dvx] -> [rows, H * dv]: each head over its root mean square (after division by
+    max(|raw[.., dv]|, exp_neg_m) + 1e-6 where exp_neg_m is given), times weight [H * dv], times act(gate)."""
+    rows, H, dvx = raw.shape
+    if act is not None and (gate is None or gate.dtype != out_dtype or gate.shape != (rows, H * dv) or gate.stride(1) != 1):
+        raise KernelError("head_norm_gate: the gate must be [rows, H * dv] of the output's dtype with unit column stride")
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != H * dv):
+        raise KernelError("head_norm_gate: the weight must be float32 [H * dv]")
+    out = torch.empty((rows, H * dv), dtype=out_dtype, device=raw.device)
+    fn = _fn("recurrent", "lq_head_norm_gate", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_p(_contig(raw, "raw")), dvx, _p(exp_neg_m), _p(weight), _p(gate), gate.stride(0) if gate is not None else 0,
+              GATES[act], _p(out), dtype_code(out_dtype), rows, H, dv, float(eps), _stream()), "head_norm_gate")
+    return out
 
 
 # ------------------------------------------------------------------ bfloat16 tensor-core kernels

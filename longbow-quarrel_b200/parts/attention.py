@@ -10,6 +10,15 @@ last w positions (start = p - w + 1, internal/device/kernels.metal:676).
 
 The three projections are one matrix product over the concatenated weight
 [(H + 2 Hkv) hd, D]; rotation and cache write are one kernel.
+
+Options that other designs use, each off by default: `bias` (q, k and v projections
+with a bias each); `value_dim` (values of another size than queries and keys); a
+position part that rotates only the first dimensions of a head; `sink` (a learned
+number per head whose exponential is one more term of the softmax denominator, with
+no key and no value: p_j = exp(s_j) / (exp(sink) + sum exp(s_j'))); `gate` ("sigmoid":
+the heads' outputs times sigmoid(W_g h) before the output projection); and
+`own_kv=False` (the layer has no keys and values: it reads the cache entry that
+another layer writes, with its own queries).
 """
 from __future__ import annotations
 
@@ -29,10 +38,12 @@ DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight
 class Attention(Mixer):
     graph_safe = True
     folds_norm = True
+    returns_branch = True
 
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, position: PartSpec | None = None, window: int | None = None,
-                 own_kv: bool = True, names: dict | None = None):
+                 own_kv: bool = True, names: dict | None = None, value_dim: int | None = None, bias: bool = False,
+                 sink: bool = False, gate: str | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if head_dim % 2 or not 2 <= head_dim <= 256:
@@ -42,13 +53,29 @@ class Attention(Mixer):
         self.runtime = runtime
         self.D, self.H, self.Hkv, self.hd = hidden_size, n_heads, n_kv_heads, head_dim
         self.scale, self.window, self.own_kv = float(scale), window, own_kv
+        self.vd = head_dim if value_dim is None else int(value_dim)
+        if not 1 <= self.vd <= 256:
+            raise ValueError(f"attention: value_dim {self.vd} must be at most 256")
+        if gate not in (None, "sigmoid"):
+            raise ValueError(f"attention: gate {gate!r} is not supported (supported: 'sigmoid')")
+        self.bias, self.sink, self.gate = bool(bias), bool(sink), gate
         self.names = {**DEFAULT_NAMES, **(names or {})}
+        for key in ("q", "k", "v"):
+            self.names.setdefault(key + "_bias", self.names[key].replace(".weight", "") + ".bias")
+        self.names.setdefault("sink", "sinks")
+        self.names.setdefault("g", "g_proj.weight")
         self.position = make_part("position", position, runtime) if position is not None else None
+        self.rot = getattr(self.position, "rotary_dims", head_dim) if self.position is not None else 0
+        # The kernels that fuse rotation and cache write into the projections, and the tensor-core attention
+        # kernels, know the plain form only; every option above takes the general kernels.
+        self.general = self.bias or self.sink or self.gate is not None or self.vd != head_dim or \
+            (self.position is not None and self.rot != head_dim)
+        self.b_qkv = self.sinks = None
         self.w_qkv: linear.LinearWeight | None = None
         self.w_o: linear.LinearWeight | None = None
 
     def cache_need(self):
-        return KVNeed(self.Hkv, self.hd, self.window)
+        return KVNeed(self.Hkv, self.hd, self.window, self.vd if self.vd != self.hd else None)
 
     def step_needs(self):
         return attention_kernels.step_needs(self.runtime.act_dtype, self.hd, self.H, self.Hkv, self.window,
@@ -56,10 +83,19 @@ class Attention(Mixer):
 
     def weights(self):
         n = self.names
-        out = {n["q"]: WeightSpec((self.H * self.hd, self.D)), n["o"]: WeightSpec((self.D, self.H * self.hd))}
+        out = {n["q"]: WeightSpec((self.H * self.hd, self.D)), n["o"]: WeightSpec((self.D, self.H * self.vd))}
         if self.own_kv:
             out[n["k"]] = WeightSpec((self.Hkv * self.hd, self.D))
-            out[n["v"]] = WeightSpec((self.Hkv * self.hd, self.D))
+            out[n["v"]] = WeightSpec((self.Hkv * self.vd, self.D))
+        if self.bias:
+            out[n["q_bias"]] = WeightSpec((self.H * self.hd,), init="small", full_precision=True)
+            if self.own_kv:
+                out[n["k_bias"]] = WeightSpec((self.Hkv * self.hd,), init="small", full_precision=True)
+                out[n["v_bias"]] = WeightSpec((self.Hkv * self.vd,), init="small", full_precision=True)
+        if self.sink:
+            out[n["sink"]] = WeightSpec((self.H,), init=("uniform", 0.0, 4.0), full_precision=True)
+        if self.gate is not None:
+            out[n["g"]] = WeightSpec((self.H * self.vd, self.D))
         if self.position is not None:
             out.update(self.position.weights())        # a position encoding may have tensors of its own
         return out
@@ -67,13 +103,47 @@ class Attention(Mixer):
     def load(self, tensors):
         n = self.names
         rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
+        if self.gate is not None:
+            rows.append(tensors[n["g"]])               # the gate's rows ride in the same product, after q, k and v
+        if len({r.dtype for r in rows}) > 1:
+            rows = [r.to(torch.float32) for r in rows]
         self.w_qkv = linear.LinearWeight(torch.cat(rows, dim=0))
+        if self.bias:
+            keys = ["q_bias"] + (["k_bias", "v_bias"] if self.own_kv else [])
+            self.b_qkv = torch.cat([tensors[n[k]].to(torch.float32) for k in keys]).contiguous()
+        if self.sink:
+            self.sinks = tensors[n["sink"]].to(torch.float32).contiguous()
         self.w_o = linear.LinearWeight(tensors[n["o"]])
         if self.position is not None and self.position.weights():
             self.position.load({name: tensors[name] for name in self.position.weights()})
 
+    def _forward_general(self, h, ctx: StepContext, cache_view, residual, store: bool):
+        """The layer with any of its options: one product for q, k, v and the gate; biases, rotation of
+        the rotated dimensions and the cache write in one kernel; attention with the sink in the
+        denominator and the gate on the way out; the output projection."""
+        H, G, hd, vd = self.H, self.Hkv, self.hd, self.vd
+        rows = linear.linear(h, self.w_qkv, self.runtime.act_dtype)
+        tables = self.position.tables() if self.position is not None else None
+        if self.position is not None and tables is None:
+            raise ValueError("attention: a position part without tables cannot be combined with the layer's options")
+        cos, sin = tables if tables is not None else (None, None)
+        v_off = (H + G) * hd
+        ops.rope_partial(rows, self.b_qkv, cos, sin, self.rot if tables is not None else 0, ctx.tok_pos, ctx.tok_seq,
+                         ctx.slots, cache_view.page_table if store else None, cache_view.k_pages if store else None,
+                         cache_view.v_pages if store else None, H + (G if self.own_kv else 0), H, G, hd, vd, v_off,
+                         cache_view.page_size)
+        g_off = H * hd + (G * (hd + vd) if self.own_kv else 0)
+        gate = rows[:, g_off:g_off + H * vd] if self.gate is not None else None
+        out = attention_kernels.attention(rows, cache_view, ctx, H, G, hd, self.scale, self.window,
+                                          next_w=self.w_o.tensor, vd=vd, sink=self.sinks, gate=gate)
+        return self._project(out, residual, None)
+
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True, emit=None):
         store = self.own_kv and writes_cache
+        if self.own_kv and not store:
+            raise ValueError("attention: a layer with its own k and v must write its cache entry")
+        if self.general:
+            return self._forward_general(h, ctx, cache_view, residual, store)
         tables = self.position.tables() if self.position is not None else None
         fused = (store and h.dtype == torch.bfloat16 and self.w_qkv.tensor.dtype == torch.bfloat16 and self.D % 8 == 0
                  and self.hd % 16 == 0 and cache_view.k_pages.dtype == torch.bfloat16 and (self.position is None or tables is not None))
@@ -110,7 +180,10 @@ class Attention(Mixer):
         return self._project(out, residual, emit)
 
     def _project(self, out, residual, emit):
-        """Output projection added into the residual; with `emit`, the next norm's rows (or None)."""
+        """Output projection added into the residual; with `emit`, the next norm's rows (or None).  Without a
+        residual the projection itself comes back, as float32 (a block that norms the branch before adding it)."""
+        if residual is None:
+            return linear.linear(out, self.w_o, torch.float32)
         if emit is None:
             linear.linear(out, self.w_o, self.runtime.act_dtype, residual=residual)
             return None

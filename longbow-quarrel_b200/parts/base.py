@@ -124,11 +124,13 @@ class KVNeed(CacheNeed):
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None        # values of another size than the keys
 
     def make_group(self, entries, sizing):
         from ..cache.paged import PagedKVGroup
         return PagedKVGroup(entries, self.n_kv_heads, self.head_dim, self.window, sizing.n_pages, sizing.page_size,
-                            sizing.max_slots, sizing.pages_per_seq, sizing.dtype, sizing.device)
+                            sizing.max_slots, sizing.pages_per_seq, sizing.dtype, sizing.device,
+                            v_head_dim=self.v_head_dim)
 
 
 @dataclass(frozen=True)
@@ -154,8 +156,12 @@ class Mixer(Part):
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache_view, residual: torch.Tensor,
                 writes_cache: bool = True) -> None:
-        """Read the normed rows h [T, D]; add the mixer's output to residual [T, D] (float32)."""
+        """Read the normed rows h [T, D]; add the mixer's output to residual [T, D] (float32).  A mixer that
+        sets `returns_branch` also takes `residual=None` and then returns its output as float32 [T, D] (for
+        an arrangement that norms the branch before it joins the stream)."""
         raise NotImplementedError
+
+    returns_branch = False
 
 
 class FeedForward(Part):

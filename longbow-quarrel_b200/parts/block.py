@@ -2,9 +2,14 @@
 
 "pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)), the order of the reference's
 block (internal/device/metal.go:1347-1527), with the residual stream x in 32-bit
-throughout (internal/engine/engine.go:1375)."""
+throughout (internal/engine/engine.go:1375).
+
+"sandwich_norm": every branch is normed on both sides, x += norm1b(mixer(norm1(x)));
+x += norm2b(ffn(norm2(x))), and a layer may have no feed-forward.  The branch's own norm,
+the addition and the norm that reads the stream next are one kernel."""
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import Part, Runtime, StepContext
 from .registry import make_part, register_part
 from .spec import LayerSpec
@@ -73,3 +78,83 @@ class PreNormBlock(Part):
             return self.ffn.forward(h, ctx, x, emit=emit)
         self.ffn.forward(h, ctx, x)
         return None
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Part):
+    """Places: norm1, mixer, norm1b, and (all three or none) norm2, ffn, norm2b.  The mixer and the
+    feed-forward hand back their outputs as float32 rows (`returns_branch`) instead of adding them."""
+
+    folds_norm = True
+
+    def __init__(self, runtime: Runtime, layer: LayerSpec):
+        self.prefix, self.runtime = layer.prefix, runtime
+        places = set(layer.parts)
+        unknown = places - {"norm1", "mixer", "norm1b", "norm2", "ffn", "norm2b"}
+        if unknown:
+            raise ValueError(f"layer {layer.prefix!r}: the arrangement 'sandwich_norm' has no place {sorted(unknown)}")
+        if len(places & {"norm2", "ffn", "norm2b"}) not in (0, 3):
+            raise ValueError(f"layer {layer.prefix!r}: norm2, ffn and norm2b come together or not at all")
+        self.norm1 = make_part("norm", layer.part("norm1"), runtime)
+        self.mixer = make_part("mixer", layer.part("mixer"), runtime)
+        self.norm1b = make_part("norm", layer.part("norm1b"), runtime)
+        self.has_ffn = "ffn" in places
+        self.norm2 = make_part("norm", layer.part("norm2"), runtime) if self.has_ffn else None
+        self.ffn = make_part("ffn", layer.part("ffn"), runtime) if self.has_ffn else None
+        self.norm2b = make_part("norm", layer.part("norm2b"), runtime) if self.has_ffn else None
+        if not getattr(self.mixer, "returns_branch", False):
+            raise ValueError(f"layer {layer.prefix!r}: the mixer {layer.part('mixer').kind!r} cannot hand back its "
+                             f"output for a norm of its own")
+        for norm in self.norms():
+            if not hasattr(norm, "gain") or not hasattr(norm, "eps"):
+                raise ValueError(f"layer {layer.prefix!r}: the arrangement 'sandwich_norm' needs RMS norms with a gain")
+
+    def norms(self):
+        return tuple(n for n in (self.norm1, self.norm1b, self.norm2, self.norm2b) if n is not None)
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm1b, self.norm2, self.ffn, self.norm2b) if p is not None)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def step_needs(self):
+        out = {}
+        for part in self.parts():
+            out.update(part.step_needs())
+        return out
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
+    def weights(self):
+        out = {}
+        for part in self.parts():
+            for name, spec in part.weights().items():
+                if name in out:
+                    raise ValueError(f"layer {self.prefix}: two parts name the tensor {name!r}")
+                out[name] = spec
+        return out
+
+    def load(self, tensors):
+        for part in self.parts():
+            part.load({n: tensors[n] for n in part.weights()})
+
+    def input_norm(self, n_rows: int):
+        """(gain, eps) of norm1: the layer ahead may make its rows in the kernel that ends it."""
+        return (self.norm1.gain, self.norm1.eps) if self.norm1.gain is not None else None
+
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool = True, normed=None, emit=None):
+        """`normed`: the rows of norm1 when the layer ahead made them; `emit`: the next layer's
+        input_norm().  Returns the next layer's rows, or None."""
+        act = self.runtime.act_dtype
+        if isinstance(normed, ops.NormedRows):
+            normed = normed.finish()
+        h = normed if normed is not None else self.norm1.forward(x)
+        y = self.mixer.forward(h, ctx, cache_view, None, writes_cache)
+        if not self.has_ffn:
+            return ops.rmsnorm_add(y, self.norm1b.gain, self.norm1b.eps, x, emit, act)
+        h = ops.rmsnorm_add(y, self.norm1b.gain, self.norm1b.eps, x, (self.norm2.gain, self.norm2.eps), act)
+        y = self.ffn.forward(h, ctx, None)
+        return ops.rmsnorm_add(y, self.norm2b.gain, self.norm2b.eps, x, emit, act)

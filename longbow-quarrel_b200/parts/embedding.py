@@ -42,7 +42,9 @@ class LinearHead(Part):
     graph_safe = True
 
     def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str, tied_to: str | None = None,
-                 tied: bool = False):
+                 tied: bool = False, softcap: float | None = None):
+        """softcap c: logits <- c tanh(logits / c)."""
+        self.softcap = float(softcap) if softcap else None
         self.runtime, self.vocab_size, self.hidden_size = runtime, vocab_size, hidden_size
         self.name, self.tied_to, self.tied = name, tied_to, tied
         self.weight: linear.LinearWeight | None = None
@@ -62,4 +64,5 @@ class LinearHead(Part):
         self.weight = linear.LinearWeight(w)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return linear.linear(h, self.weight, torch.float32)
+        logits = linear.linear(h, self.weight, torch.float32)
+        return ops.softcap(logits, self.softcap) if self.softcap else logits

@@ -15,15 +15,17 @@ from .registry import register_part
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, runtime: Runtime, size: int, eps: float, name: str = "weight"):
-        self.runtime, self.size, self.eps, self.name = runtime, size, float(eps), name
+    def __init__(self, runtime: Runtime, size: int, eps: float, name: str = "weight", offset: float = 0.0):
+        """offset: what is added to the stored tensor to give the gain (1 for checkpoints that keep their
+        gains minus one: y = x / rms(x) * (1 + w)); the sum is made once, in 32-bit, when the tensor is loaded."""
+        self.runtime, self.size, self.eps, self.name, self.offset = runtime, size, float(eps), name, float(offset)
         self.gain: torch.Tensor | None = None
 
     def weights(self):
-        return {self.name: WeightSpec((self.size,), init="gain", full_precision=True)}
+        return {self.name: WeightSpec((self.size,), init="gain" if self.offset == 0.0 else "small", full_precision=True)}
 
     def load(self, tensors):
-        self.gain = tensors[self.name].to(torch.float32).contiguous()
+        self.gain = (tensors[self.name].to(torch.float32) + self.offset).contiguous()
 
     def forward(self, x, rows=None):
         return ops.rmsnorm(x, self.gain, self.eps, self.runtime.act_dtype, rows)

@@ -7,10 +7,15 @@ wavelength: kept above the high-frequency bound, divided by `factor` below the
 low-frequency bound, blended in between.  Frequencies and angles are worked out in
 float64 on the host and tabulated as float32 cos/sin, so every kernel and every
 way of cutting the work reads the same angles.
+
+`rotary_dims` r < head_dim rotates only the first r dimensions of a head (pairs i,
+i + r/2, f_i = theta^(-2i/r)); the tables are then [positions, r/2].  `scaling` may
+also be a `LinearScaling(factor)`: every f_i divided by the factor.
 """
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 
 import torch
 
@@ -18,12 +23,20 @@ from .base import PositionEncoding, Runtime
 from .registry import register_part
 
 
+@dataclass(frozen=True)
+class LinearScaling:
+    """Positions stretched by `factor`: every frequency is divided by it."""
+    factor: float
+
+
 def rope_frequencies(head_dim: int, theta: float, scaling=None) -> torch.Tensor:
-    """f_i for i < head_dim / 2, float64."""
+    """f_i for i < head_dim / 2, float64 (head_dim: the number of rotated dimensions)."""
     i = torch.arange(head_dim // 2, dtype=torch.float64)
     f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / head_dim)
     if scaling is None:
         return f
+    if isinstance(scaling, LinearScaling):
+        return f / float(scaling.factor)
     n0 = float(scaling.original_max_position_embeddings)
     lo, hi, factor = float(scaling.low_freq_factor), float(scaling.high_freq_factor), float(scaling.factor)
     wavelen = 2.0 * math.pi / f
@@ -37,15 +50,18 @@ def rope_frequencies(head_dim: int, theta: float, scaling=None) -> torch.Tensor:
 class Rope(PositionEncoding):
     graph_safe = True
 
-    def __init__(self, runtime: Runtime, head_dim: int, theta: float, scaling=None):
+    def __init__(self, runtime: Runtime, head_dim: int, theta: float, scaling=None, rotary_dims: int | None = None):
         self.runtime, self.head_dim, self.theta, self.scaling = runtime, head_dim, float(theta), scaling
+        self.rotary_dims = head_dim if rotary_dims is None else int(rotary_dims)
+        if self.rotary_dims % 2 or not 0 < self.rotary_dims <= head_dim:
+            raise ValueError(f"rope: {self.rotary_dims} rotated dimensions must be even and at most head_dim {head_dim}")
         self._tables = None
 
     def tables(self):
         if self._tables is None:
-            key = ("rope", self.head_dim, self.theta, self.scaling, self.runtime.max_context)
+            key = ("rope", self.rotary_dims, self.theta, self.scaling, self.runtime.max_context)
             if key not in self.runtime.shared:
-                f = rope_frequencies(self.head_dim, self.theta, self.scaling)
+                f = rope_frequencies(self.rotary_dims, self.theta, self.scaling)
                 pos = torch.arange(self.runtime.max_context, dtype=torch.float64)
                 ang = pos[:, None] * f[None, :]
                 self.runtime.shared[key] = (torch.cos(ang).to(torch.float32).to(self.runtime.device).contiguous(),

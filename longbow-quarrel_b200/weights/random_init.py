@@ -33,6 +33,11 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, dtype: torch.dtype, de
         if gain_std:
             t += gain_std * torch.randn(spec.shape, generator=gen, device=device, dtype=torch.float32)
         return t.to(dtype)
+    if spec.init == "small":
+        return (gain_std * torch.randn(spec.shape, generator=gen, device=device, dtype=torch.float32)).to(dtype)
+    if isinstance(spec.init, tuple) and spec.init[0] == "uniform":
+        lo, hi = float(spec.init[1]), float(spec.init[2])
+        return (lo + (hi - lo) * torch.rand(spec.shape, generator=gen, device=device, dtype=torch.float32)).to(dtype)
     # Large tensors are drawn in the target dtype to keep the peak memory at one copy.
     draw = torch.float32 if spec.shape and _numel(spec.shape) < (1 << 26) else dtype
     t = torch.randn(spec.shape, generator=gen, device=device, dtype=draw)

@@ -9,8 +9,9 @@ class WeightSpec:
     """One tensor a part reads from the checkpoint.
 
     shape     the exact shape it must have.
-    init      how the random-weights mode fills it: "normal" (N(0, std)) or "gain"
-              (1 + N(0, gain_std)).
+    init      how the random-weights mode fills it: "normal" (N(0, std)), "gain"
+              (1 + N(0, gain_std)), "small" (N(0, gain_std): offsets of gains from one, biases), or
+              ("uniform", lo, hi).
     fallback  full name of another tensor that stands in when this one is absent
               (a tied output head reads the embedding table).
     integer   the tensor is an integer table (kept as int32).
@@ -18,7 +19,7 @@ class WeightSpec:
               gains): a loader that converts tensors to the model's precision leaves it as stored.
     """
     shape: tuple[int, ...]
-    init: str = "normal"
+    init: str | tuple = "normal"
     fallback: str | None = None
     integer: bool = False
     full_precision: bool = False
