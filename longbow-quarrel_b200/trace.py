@@ -52,8 +52,7 @@ def main(argv=None) -> int:
     import torch
     from longbow_quarrel_b200.engine import Engine
 
-    # A few pages more than asked for: every live request may leave the end of its last page unused.
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 4 * 64)
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
     layer_rms: list = []
     if args.layer_stats:
         def probe(run, x, ctx):
