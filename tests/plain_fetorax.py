@@ -21,7 +21,6 @@ t: a position counted from 0, D_h: a head's key size):
 from __future__ import annotations
 
 import json
-import math
 import struct
 from pathlib import Path
 
@@ -53,6 +52,14 @@ def load_folder(folder):
 
 # --------------------------------------------------------------------------- small pieces
 
+_STORAGE = None        # set by forward(storage=...): the dtype in which activations are kept between operations
+
+
+def _st(x: torch.Tensor) -> torch.Tensor:
+    """x as an engine that stores its activations in `_STORAGE` would hand it on (the yardstick for bfloat16)."""
+    return x if _STORAGE is None else x.to(_STORAGE).to(x.dtype)
+
+
 def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
@@ -63,8 +70,8 @@ def offset_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def relu_squared_ffn(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
-    a = torch.clamp(h @ up.T, min=0.0)
-    return (a * a) @ down.T
+    a = torch.clamp(_st(h @ up.T), min=0.0)
+    return _st(a * a) @ down.T
 
 
 def rotary_frequencies(dims: int, base: float, factor: float | None) -> torch.Tensor:
@@ -97,7 +104,7 @@ def attention_keys_values(h, m: dict, w: dict, pre: str):
     G, dk, dv = m["kv_heads"], m["dim"], m["vdim"]
     k = (h @ w[pre + "k"].T + w[pre + "k.b"]).reshape(T, G, dk)
     v = (h @ w[pre + "v"].T + w[pre + "v.b"]).reshape(T, G, dv)
-    return rotate(k, torch.arange(T), m.get("rot")), v
+    return _st(rotate(k, torch.arange(T), m.get("rot"))), _st(v)
 
 
 def sink_attention(h, m: dict, w: dict, pre: str, k, v) -> torch.Tensor:
@@ -105,7 +112,7 @@ def sink_attention(h, m: dict, w: dict, pre: str, k, v) -> torch.Tensor:
     head's denominator, gated by sigmoid(W_g h) before the output projection."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = rotate((h @ w[pre + "q"].T + w[pre + "q.b"]).reshape(T, H, dk), torch.arange(T), m.get("rot"))
+    q = _st(rotate((h @ w[pre + "q"].T + w[pre + "q.b"]).reshape(T, H, dk), torch.arange(T), m.get("rot")))
     out = torch.zeros(T, H, dv, dtype=h.dtype)
     for head in range(H):
         g = head // (H // G)
@@ -115,17 +122,17 @@ def sink_attention(h, m: dict, w: dict, pre: str, k, v) -> torch.Tensor:
             top = torch.maximum(s.max(), sink)
             e = torch.exp(s - top)
             out[t, head] = (e[:, None] * v[:t + 1, g]).sum(0) / (e.sum() + torch.exp(sink - top))
-    gate = torch.sigmoid(h @ w[pre + "g"].T)
-    return (out.reshape(T, H * dv) * gate) @ w[pre + "o"].T
+    gate = torch.sigmoid(_st(h @ w[pre + "g"].T))
+    return _st(out.reshape(T, H * dv) * gate) @ w[pre + "o"].T
 
 
 def retention(h, m: dict, w: dict, pre: str, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
     pos = torch.arange(T)
-    q = rotate((h @ w[pre + "q"].T).reshape(T, H, dk), pos, m.get("rot"))
-    k = rotate((h @ w[pre + "k"].T).reshape(T, H, dk), pos, m.get("rot")) * dk ** -0.5
-    v = (h @ w[pre + "v"].T).reshape(T, H, dv)
+    q = rotate(_st(h @ w[pre + "q"].T).reshape(T, H, dk), pos, m.get("rot"))
+    k = rotate(_st(h @ w[pre + "k"].T).reshape(T, H, dk), pos, m.get("rot")) * dk ** -0.5
+    v = _st(h @ w[pre + "v"].T).reshape(T, H, dv)
     out = torch.zeros(T, H, dv, dtype=h.dtype)
     for head in range(H):
         S = torch.zeros(dk, dv, dtype=h.dtype)
@@ -133,15 +140,15 @@ def retention(h, m: dict, w: dict, pre: str, eps: float) -> torch.Tensor:
             S = m["decay"][head] * S + torch.outer(k[t, head], v[t, head])
             out[t, head] = S.T @ q[t, head]
     out = unit_rms(out, eps).reshape(T, H * dv)
-    return (out * torch.nn.functional.silu(h @ w[pre + "g"].T)) @ w[pre + "o"].T
+    return _st(out * torch.nn.functional.silu(_st(h @ w[pre + "g"].T))) @ w[pre + "o"].T
 
 
 def mlstm(h, m: dict, w: dict, pre: str, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, dk, dv, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
-    q = (h @ w[pre + "q"].T).reshape(T, H, dk) * dk ** -0.5
-    k = (h @ w[pre + "k"].T).reshape(T, H, dk)
-    v = (h @ w[pre + "v"].T).reshape(T, H, dv)
+    q = _st(h @ w[pre + "q"].T).reshape(T, H, dk) * dk ** -0.5
+    k = _st(h @ w[pre + "k"].T).reshape(T, H, dk)
+    v = _st(h @ w[pre + "v"].T).reshape(T, H, dv)
     log_i = cap * torch.tanh((h @ w[pre + "i"].T + w[pre + "i.b"]) / cap)                                     # [T, H]
     log_f = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ w[pre + "f"].T + w[pre + "f.b"]) / cap))
     out = torch.zeros(T, H, dv, dtype=h.dtype)
@@ -155,20 +162,33 @@ def mlstm(h, m: dict, w: dict, pre: str, eps: float) -> torch.Tensor:
             mx = new_mx
             out[t, head] = S.T @ q[t, head] / (torch.maximum(torch.abs(n @ q[t, head]), torch.exp(-mx)) + 1e-6)
     out = unit_rms(out, eps).reshape(T, H * dv) * w[pre + "norm"]
-    return (out * torch.sigmoid(h @ w[pre + "g"].T)) @ w[pre + "o"].T
+    return _st(out * torch.sigmoid(_st(h @ w[pre + "g"].T))) @ w[pre + "o"].T
 
 
 # --------------------------------------------------------------------------- the model
 
-def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, layers_out: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence; `layers_out` collects the residual stream after every layer."""
+def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, layers_out: list | None = None,
+            storage=None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence; `layers_out` collects the residual stream after every layer.
+    storage=torch.bfloat16 rounds what an engine of that precision keeps between its operations (the rows a
+    norm hands on, projections, a mixer's output before its last product, the feed-forward's hidden rows);
+    the residual stream, the norms, scores and states stay exact."""
+    global _STORAGE
+    _STORAGE = storage
+    try:
+        return _forward(cfg, weights, tokens, dtype, layers_out)
+    finally:
+        _STORAGE = None
+
+
+def _forward(cfg, weights, tokens, dtype, layers_out):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     kept: dict[int, tuple] = {}
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
-        h = offset_norm(x, w[p + "norm1"], eps)
+        h = _st(offset_norm(x, w[p + "norm1"], eps))
         kind = layer["type"]
         if kind == "attention":
             src = m.get("kv_from")
@@ -184,11 +204,11 @@ def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, layers_out: l
             raise ValueError(f"layer {i}: unknown mixer {kind!r}")
         x = x + offset_norm(y, w[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            h = offset_norm(x, w[p + "norm2"], eps)
+            h = _st(offset_norm(x, w[p + "norm2"], eps))
             x = x + offset_norm(relu_squared_ffn(h, w[p + "mlp.up"], w[p + "mlp.down"]), w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    z = offset_norm(x, w["final.norm"], eps) @ w["head"].T
+    z = _st(offset_norm(x, w["final.norm"], eps)) @ w["head"].T
     return softcap(z, cfg.get("logit_softcap"))
 
 

@@ -1,0 +1,196 @@
+"""The Fetorax design through the engine: every mixer alone and together, every way of cutting and
+batching requests, slots and pages used again, long decoding, generation through the entry point and
+the command line -- each against the plain implementation (tests/plain_fetorax.py)."""
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_fetorax
+from fetorax_models import CONFIGS, F32_TOL, bound, load, make_folder, row_errors, tokens
+from trace_tools import ROOT, Trace, run_trace, split, trace_batches, trace_chunked, trace_last_one_by_one, trace_mixed, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def _engine(folder, dtype, **kw):
+    from longbow_quarrel_b200.engine import Engine
+    return Engine.from_pretrained(folder, dtype=dtype, **kw)
+
+
+def _plain(folder, toks):
+    cfg, weights = load(folder)
+    return cfg, weights, plain_fetorax.forward(cfg, weights, toks).numpy()
+
+
+def _check(got: dict, requests: dict, folder, dtype: str, what: str, factor: float = 1.0):
+    for rid, toks in requests.items():
+        cfg, weights, ref = _plain(folder, toks)
+        tol = factor * bound(dtype, cfg, weights, toks, ref)
+        keys = [k for k in got if k[0] == rid]
+        assert keys, f"{what}: nothing came back for {rid}"
+        for _, pos in keys:
+            err = float(row_errors(got[(rid, pos)], ref[pos]))
+            assert err < tol, f"{what}: request {rid} position {pos} of {len(toks)}: error {err:.3g}, bound {tol:.3g}"
+
+
+# ------------------------------------------------------------------ each mixer alone
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["only_attention", "only_retention", "only_mlstm"])
+def test_one_layer_of_each_mixer_whole_and_token_by_token(tmp_path, name, dtype):
+    """A model of one layer: the whole prompt in one step (its first tokens included), and the same tokens one
+    by one from the first (133 steps: across two page borders, replayed from a captured step)."""
+    folder = make_folder(tmp_path, name, seed=3)
+    toks = tokens(133, CONFIGS[name]["vocab"], 5)
+    cfg, weights, ref = _plain(folder, toks)
+    tol = bound(dtype, cfg, weights, toks, ref)
+    eng = _engine(folder, dtype, max_tokens=512)
+    s = eng.new_sequence()
+    whole = eng.step([(s, toks)], [list(range(len(toks)))]).cpu().numpy()
+    eng.end_sequence(s)
+    assert row_errors(whole, ref).max() < tol
+    s = eng.new_sequence()
+    single = np.stack([eng.step([(s, [t])], [[0]]).cpu().numpy()[0] for t in toks])
+    eng.end_sequence(s)
+    assert row_errors(single, ref).max() < tol
+    # Prompt and single tokens go through the same recurrence and the same order of sums.
+    assert row_errors(single, whole).max() < (F32_TOL if dtype == "float32" else tol)
+    eng.close()
+
+
+# ------------------------------------------------------------------ whole models, every cut, through the replay program
+
+LENGTHS = {"r0": 70, "r1": 33, "r2": 140, "r3": 65, "r4": 64, "r5": 34, "r6": 129}
+PROMPTS = {"r0": 7, "r1": 1, "r2": 100, "r3": 2, "r4": 63, "r5": 20, "r6": 65}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd", "head64"])
+def test_every_cut_of_every_request_matches_plain(tmp_path, name, dtype):
+    """Whole; the last 32 tokens one by one; batches of three unequal requests that go on together, the shorter
+    ending earlier, the next batch in the slots and pages given back; portions of 2, 3, 59, 1, 64 and 7 tokens;
+    steps that mix portions with single tokens.  One call of the replay program runs them one after the other."""
+    folder = make_folder(tmp_path, name, seed=11)
+    vocab = CONFIGS[name]["vocab"]
+    requests = {rid: tokens(n, vocab, 100 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+    tr = Trace()
+    tr.extend(trace_whole(requests), "whole:")
+    tr.extend(trace_last_one_by_one(requests), "tail:")
+    tr.extend(trace_batches(requests, PROMPTS, width=3), "batched:")
+    tr.extend(trace_chunked(requests, [2, 3, 59, 1, 64, 7]), "portions:")
+    tr.extend(trace_mixed(requests, PROMPTS, [5, 1, 2, 1, 17]), "mixed:")
+    got = run_trace(folder, dtype, tr, tmp_path / "out")
+    cuts = {p: split(got, p + ":") for p in ("whole", "tail", "batched", "portions", "mixed")}
+    for what, rows in cuts.items():
+        assert len(rows) == (33 * len(requests) if what == "tail" else sum(LENGTHS.values())), what
+        _check(rows, requests, folder, dtype, what)
+    # The cuts against one another: in float32 to 2e-5, in bfloat16 within the same noise.
+    for what in ("tail", "batched", "portions", "mixed"):
+        for (rid, pos), row in cuts[what].items():
+            if dtype == "float32":
+                err = float(row_errors(row, cuts["whole"][(rid, pos)]))
+                assert err < F32_TOL, f"{what} against whole: {rid} position {pos}: {err:.3g}"
+
+
+# ------------------------------------------------------------------ slots and pages used again, long decoding
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_slot_that_is_used_again_starts_from_nothing(tmp_path, dtype):
+    """One slot and just enough pages: each request runs in what the one before it gave back, so a state or a
+    key that outlived its request would show in the next one's first tokens."""
+    folder = make_folder(tmp_path, "mixed", seed=21)
+    eng = _engine(folder, dtype, max_tokens=192, max_batch=1)
+    for i, n in enumerate([150, 3, 130, 66]):
+        toks = tokens(n, CONFIGS["mixed"]["vocab"], 300 + i)
+        cfg, weights, ref = _plain(folder, toks)
+        s = eng.new_sequence()
+        assert s == 0
+        cut = max(1, n - 40)
+        rows = [eng.step([(s, toks[:cut])], [list(range(cut))]).cpu().numpy()]
+        rows += [eng.step([(s, [t])], [[0]]).cpu().numpy() for t in toks[cut:]]
+        eng.end_sequence(s)
+        assert row_errors(np.concatenate(rows), ref).max() < bound(dtype, cfg, weights, toks, ref), f"request {i}"
+    assert eng.cache.pages_in_use() == 0
+    eng.close()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_from_the_first_token(tmp_path, dtype):
+    """400 single-token steps of three sequences side by side (captured once, replayed): the recurrent states
+    and a far key are carried over hundreds of steps and several page borders."""
+    folder = make_folder(tmp_path, "head64", seed=31)
+    vocab = CONFIGS["head64"]["vocab"]
+    seqs = [tokens(400, vocab, 40), tokens(400, vocab, 41), tokens(260, vocab, 42)]
+    eng = _engine(folder, dtype, max_tokens=3 * 448)
+    slots = [eng.new_sequence() for _ in seqs]
+    last = {}
+    for t in range(400):
+        live = [i for i, q in enumerate(seqs) if t < len(q)]
+        out = eng.step([(slots[i], [seqs[i][t]]) for i in live], [[0]] * len(live)).cpu().numpy()
+        for row, i in zip(out, live):
+            last[(i, t)] = row
+        for i in live:
+            if t == len(seqs[i]) - 1:
+                eng.end_sequence(slots[i])
+    for i, q in enumerate(seqs):
+        cfg, weights, ref = _plain(folder, q)
+        tol = bound(dtype, cfg, weights, q, ref)
+        for t in (0, 1, 63, 64, 65, 127, 128, 255, 256, len(q) - 1):
+            assert float(row_errors(last[(i, t)], ref[t])) < tol, (i, t)
+    eng.close()
+
+
+# ------------------------------------------------------------------ generation through the entry point and the command line
+
+def _greedy_matches(folder, prompt, new, dtype):
+    cfg, weights = load(folder)
+    seq = list(prompt)
+    for tok in new:
+        logits = plain_fetorax.forward(cfg, weights, seq)[-1].numpy()
+        best = int(np.argmax(logits))
+        gap = (logits[best] - logits[tok]) / np.sqrt((logits ** 2).mean())
+        assert tok == best or (dtype == "bfloat16" and gap < 5e-2), (dtype, len(seq), tok, best, gap)
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_scheduler(tmp_path, dtype):
+    """Engine.generate: unequal prompts in batches of three (the second batch in the first one's slots), greedy."""
+    from longbow_quarrel_b200.sampling import SamplingParams
+    folder = make_folder(tmp_path, "mixed", seed=41)
+    vocab = CONFIGS["mixed"]["vocab"]
+    prompts = [tokens(n, vocab, 500 + i) for i, n in enumerate([9, 1, 70, 2, 64])]
+    eng = _engine(folder, dtype, max_tokens=3 * 128, max_batch=3)
+    out = eng.generate(prompts, max_new_tokens=10, sampling=SamplingParams(temperature=0.0), stop_ids=[], batch_size=3)
+    assert [len(o) for o in out] == [10] * 5
+    for prompt, new in zip(prompts, out):
+        _greedy_matches(folder, prompt, new, dtype)
+    eng.close()
+
+
+def test_the_command_line_generates_with_a_fetorax_folder(tmp_path):
+    folder = make_folder(tmp_path, "odd", seed=51)
+    prompt = tokens(12, CONFIGS["odd"]["vocab"], 7)
+    proc = subprocess.run([str(ROOT / "bin" / "quarrel"), "-model", str(folder), "-prompt-ids", ",".join(map(str, prompt)),
+                           "-n", "6", "-temp", "0", "-penalty", "1.0", "-dtype", "float32", "-output", "json"],
+                          capture_output=True, text=True, timeout=600, env={**__import__("os").environ, "LQ_PYTHON": sys.executable})
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    new = json.loads(proc.stdout.strip().splitlines()[-1])["output"][0]
+    assert len(new) == 6
+    _greedy_matches(folder, prompt, new, "float32")
+
+
+def test_random_weights_from_a_configuration(tmp_path):
+    """Engine.from_config builds the design from a dict with config.json's keys."""
+    from longbow_quarrel_b200.engine import Engine
+    from longbow_quarrel_b200.sampling import SamplingParams
+    eng = Engine.from_config(CONFIGS["head64"], seed=3, max_tokens=256, max_batch=2)
+    out = eng.generate([[1, 2, 3], [4]], max_new_tokens=5, sampling=SamplingParams(temperature=0.0), stop_ids=[])
+    assert [len(o) for o in out] == [5, 5]
+    eng.close()

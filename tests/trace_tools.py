@@ -170,7 +170,8 @@ def run_trace(model_dir: Path, dtype: str, trace: Trace, out_dir: Path, max_toke
     assert proc.returncode == 0, f"trace_run failed ({proc.returncode}):\n{proc.stderr[-4000:]}"
     done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
     assert done == [f"done {s['step']}" for s in trace.steps], proc.stdout[-2000:]
-    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    config = json.loads((Path(model_dir) / "config.json").read_text())
+    vocab = config["vocab_size"] if "vocab_size" in config else config["vocab"]
     result = {}
     for step, rows in trace.rows.items():
         data = np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(rows), vocab)
