@@ -70,7 +70,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
                    int n_splits, int part_stride, const int* __restrict__ work, const char* next_w, unsigned next_piece,
-                   int early_loads) {
+                   int early_loads, const float* __restrict__ sink) {
     constexpr int LD = HD + PAD;                   // shared-memory row length in elements
     constexpr int KD = HD / 16;                    // k16 steps over the head dimension
     constexpr int STAGE = 2 * TILE * LD;           // elements of one tile: K rows, then V rows
@@ -313,6 +313,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         }
         int h = kvh * G + gt * 16 + r;
         if (parts == 1) {
+            // sink (optional): one more term exp(sink[h]) in the head's denominator, with no key and no value
+            if (sink) l += expf(sink[h] - mx);
             out[((size_t)tok * H + h) * hd + d] = __float2bfloat16_rn(acc / l);
         } else {
             size_t base = ((size_t)tok * H + h) * part_stride + split;
@@ -341,7 +343,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         const float ls = lane < parts ? __ldcg(ml + 2 * lane + 1) : 0.f;
         const float mx = warp_max(m);
         const float w = m > -CUDART_INF_F ? expf(m - mx) : 0.f;
-        const float l = warp_sum(ls * w);        // the same order of additions whichever block merges
+        float l = warp_sum(ls * w);        // the same order of additions whichever block merges
+        if (sink) l += expf(sink[kvh * G + gt * 16 + r] - mx);
         if (lane < parts) sm_w[r][lane] = w;
         if (lane == 0) sm_inv[r] = 1.0f / l;
     }
@@ -360,7 +363,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
 
 // Merge the slices of one (token, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M).
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  __nv_bfloat16* __restrict__ out, int hd, int n_splits) {
+                                  __nv_bfloat16* __restrict__ out, int hd, int n_splits, int H,
+                                  const float* __restrict__ sink) {
     __shared__ float w[MAX_SPLITS];
     __shared__ float inv;
     const size_t th = blockIdx.x;
@@ -373,7 +377,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
         const float ls = lane < n_splits ? ml[2 * lane + 1] : 0.f;
         const float mx = warp_max(m);
         const float f = m > -CUDART_INF_F ? expf(m - mx) : 0.f;
-        const float l = warp_sum(ls * f);
+        float l = warp_sum(ls * f);
+        if (sink) l += expf(sink[th % H] - mx);
         if (lane < n_splits) w[lane] = f;
         if (lane == 0) inv = 1.0f / l;
     }
@@ -390,7 +395,8 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
            const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, int* counters,
            void* out, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
-           const int* work, int teams, const void* next_w, long next_bytes, int early_loads, cudaStream_t stream) {
+           const int* work, int teams, const void* next_w, long next_bytes, int early_loads, const float* sink,
+           cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
     if (work) grid = dim3(Hkv * gtiles, teams, 1);      // n_splits is then the room for parts per token in the scratch
@@ -410,10 +416,10 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
         part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits, n_splits, work,
-        (const char*)next_w, (unsigned)piece, early_loads);
+        (const char*)next_w, (unsigned)piece, early_loads, sink);
     if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;
     return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
-                      (__nv_bfloat16*)out, hd, n_splits);
+                      (__nv_bfloat16*)out, hd, n_splits, H, sink);
 }
 
 }  // namespace
@@ -442,23 +448,36 @@ bool sizes_ok(int H, int Hkv, int hd, int page_size, int q_stride, int n_splits)
 // five integers a segment; the grid is then one block per (kv head, row tile, team), n_splits is the
 // room for one token's parts in the scratch (part_o: T*H*n_splits*hd floats), no token may have more
 // parts than that, and the counters are required when any token has more than one part.
-LQ_EXPORT int lq_attn_decode_work(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+//
+// sink (or null): float32 [H]; each head's softmax denominator gets one more term exp(sink[h]).
+LQ_EXPORT int lq_attn_decode_sink(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                   const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                   const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
                                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
                                   const int* work, int teams, const void* next_w, long next_bytes, int early_loads,
-                                  cudaStream_t stream) {
+                                  const float* sink, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (!sizes_ok(H, Hkv, hd, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
     if (work && (teams < 1 || teams > 65535 || (n_splits > 1 && !counters))) return LQ_BAD_SIZE;
 #define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
                                     part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
-                                    work, teams, next_w, next_bytes, early_loads, stream)
+                                    work, teams, next_w, next_bytes, early_loads, sink, stream)
     if (hd <= 32) LQ_GO(32);
     if (hd <= 64) LQ_GO(64);
     LQ_GO(128);
 #undef LQ_GO
+}
+
+LQ_EXPORT int lq_attn_decode_work(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                  const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
+                                  int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+                                  const int* work, int teams, const void* next_w, long next_bytes, int early_loads,
+                                  cudaStream_t stream) {
+    return lq_attn_decode_sink(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o, part_ml,
+                               counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, work, teams, next_w,
+                               next_bytes, early_loads, nullptr, stream);
 }
 
 LQ_EXPORT int lq_attn_decode_next(const void* q, int q_stride, const void* k_pages, const void* v_pages,

@@ -56,7 +56,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                     const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
                     const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
-                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, float scale_log2, int window) {
+                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, float scale_log2, int window, const float* __restrict__ sink) {
     constexpr int LD = HD + PAD;                       // shared-memory row length in elements
     constexpr int KD = HD / 16;                        // k16 steps over the head dimension
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -212,6 +212,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sink) {
+        // One more term exp(sink[h]) in the head's denominator, with no key and no value (m and l are in powers of two).
+        const float sk = sink[h] * 1.4426950408889634f;
+        l0 += exp2f(sk - m0);
+        l1 += exp2f(sk - m1);
+    }
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) {
@@ -232,7 +238,7 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
            const int* slots, const int* kv_len, const int* qb_seq, const int* qb_row, const int* qb_rows,
            const int* qb_pos, void* out, int n_blocks, int H, int Hkv, int hd, float scale, int window,
-           cudaStream_t stream) {
+           const float* sink, cudaStream_t stream) {
     constexpr size_t smem = (size_t)(BLOCK_M + 4 * BLOCK_N) * (HD + PAD) * 2;
     static bool configured = false;
     if (!configured) {
@@ -243,7 +249,7 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     dim3 grid(n_blocks * H);
     return launch_pdl(attn_prefill_kernel<HD>, grid, dim3(NT), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
-        qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv, hd, scale * 1.4426950408889634f, window);
+        qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv, hd, scale * 1.4426950408889634f, window, sink);
 }
 
 }  // namespace
@@ -251,15 +257,16 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
 // q: rows of q_stride elements whose first H*hd hold the query heads; out [T, H*hd].
 // qb_*: the work list, n_blocks entries: sequence, first packed row, rows (<= 64), position of the first row.
 // head_dim a multiple of 8 and at most 128; the cache's page size must be 64.
+// sink (or null): float32 [H]; each head's softmax denominator gets one more term exp(sink[h]).
 LQ_EXPORT int lq_attn_prefill(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                               const int* page_table, int pt_stride, const int* slots, const int* kv_len,
                               const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
                               int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
-                              cudaStream_t stream) {
+                              const float* sink, cudaStream_t stream) {
     if (n_blocks <= 0) return LQ_OK;
     if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size != BLOCK_N || q_stride % 8) return LQ_BAD_SIZE;
 #define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row, \
-                                    qb_rows, qb_pos, out, n_blocks, H, Hkv, hd, scale, window, stream)
+                                    qb_rows, qb_pos, out, n_blocks, H, Hkv, hd, scale, window, sink, stream)
     if (hd <= 32) LQ_GO(32);
     if (hd <= 64) LQ_GO(64);
     LQ_GO(128);

@@ -91,7 +91,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_stride,
                        const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
                        const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
-                       __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window) {
+                       __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window,
+                        const float* __restrict__ sink) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int DH = HD / 64;                  // panels of 64 elements along the head dimension
     Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -308,6 +309,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float total = 0.f;
 #pragma unroll
             for (int q = 0; q < PARTS; ++q) total += sm.row_sum[q][r];
+            // sink (optional): one more term exp(sink[h]) in the denominator (sums are in powers of two, relative to m_ref)
+            if (sink) total += ex2(fmaf(sink[h], 1.4426950408889634f, m_ref == -CUDART_INF_F ? 0.f : -m_ref));
             const float inv = 1.0f / total;
             __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD + part * OC;
 #pragma unroll 1
@@ -364,7 +367,8 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_stride,
                         const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
                         const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
-                        __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window) {
+                        __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window,
+                        const float* __restrict__ sink) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int DH = HD / 64;
     Smem2<HD>& sm = *reinterpret_cast<Smem2<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -551,6 +555,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         if (ok) {
             fence_after();
+            if (sink) l += ex2(fmaf(sink[h], 1.4426950408889634f, m_ref == -CUDART_INF_F ? 0.f : -m_ref));
             const float inv = 1.0f / l;
             __nv_bfloat16* orow = out + ((size_t)(row0 + r) * H + h) * HD;
 #pragma unroll 1
@@ -585,7 +590,7 @@ template <int HD>
 int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages, int n_pages,
               const int* page_table, int pt_stride, const int* slots, const int* kv_len, const int* qb_seq,
               const int* qb_row, const int* qb_rows, const int* qb_pos, void* out, int n_blocks, int H, int Hkv,
-              float scale, int window, cudaStream_t stream) {
+              float scale, int window, const float* sink, cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
     const long kv_rows = (long)n_pages * Hkv * PAGE;
     int rc = make_map_bf16(&mq, q, T, q_stride, q_stride, BM);
@@ -612,29 +617,30 @@ int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const voi
         }
         return launch_pdl(attn_prefill_two_kernel<HD>, dim3(n_blocks * (H / 2)), dim3(N_THREADS2), smem2, stream, mq, mk, mv,
                           page_table, pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
-                          (int)kv_rows, scale * 1.4426950408889634f, window);
+                          (int)kv_rows, scale * 1.4426950408889634f, window, sink);
     }
     return launch_pdl(attn_prefill_tc_kernel<HD>, dim3(n_blocks * H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
                       pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
-                      (int)kv_rows, scale * 1.4426950408889634f, window);
+                      (int)kv_rows, scale * 1.4426950408889634f, window, sink);
 }
 }  // namespace
 
 // q: [T, q_stride] bfloat16 rows whose first H*hd elements hold the query heads; out [T, H*hd].  hd is 64 or 128.
 // k_pages, v_pages: [n_pages, Hkv, 64, hd] bfloat16 of one cache entry, finite everywhere.
 // qb_*: the work list, n_blocks entries: sequence, first packed row, rows (<= 128), position of the first row.
+// sink (or null): float32 [H]; each head's softmax denominator gets one more term exp(sink[h]).
 LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages,
                                  int n_pages, const int* page_table, int pt_stride, const int* slots, const int* kv_len,
                                  const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
                                  int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
-                                 cudaStream_t stream) {
+                                 const float* sink, cudaStream_t stream) {
     if (n_blocks <= 0) return LQ_OK;
     if ((hd != 64 && hd != 128) || page_size != PAGE || H % Hkv || q_stride % 8 || ((uintptr_t)q & 15)) return LQ_BAD_SIZE;
     if (hd == 64)
         return launch_hd<64>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
-                             qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, stream);
+                             qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, sink, stream);
     return launch_hd<128>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
-                          qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, stream);
+                          qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, sink, stream);
 }
 
 LQ_EXPORT int lq_attn_prefill_tc_status() { return tc::status_read(); }

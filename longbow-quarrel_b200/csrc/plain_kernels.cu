@@ -526,6 +526,31 @@ LQ_EXPORT int lq_activation(const void* x, void* out, int dtype, long long total
     return LQ_BAD_DTYPE;
 }
 
+// x[r, c] *= sigmoid(gate[r, c]) (act 1) or silu(gate[r, c]) (act 2), in place; gate rows may be strided.
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int cols, size_t total, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float g = to_f32(gate[(i / cols) * gate_stride + i % cols]);
+    const float sg = 1.f / (1.f + expf(-g));
+    x[i] = from_f32<T>(to_f32(x[i]) * (act == 1 ? sg : g * sg));
+}
+
+LQ_EXPORT int lq_gate_mul(void* x, const void* gate, int gate_stride, int dtype, int rows, int cols, int act, cudaStream_t stream) {
+    const size_t total = (size_t)rows * cols;
+    if (total == 0) return LQ_OK;
+    if (act != 1 && act != 2) return LQ_BAD_SIZE;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == LQ_F32)
+        return launch_pdl(gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride, cols, total, act);
+    if (dtype == LQ_BF16)
+        return launch_pdl(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x,
+                          (const __nv_bfloat16*)gate, gate_stride, cols, total, act);
+    return LQ_BAD_DTYPE;
+}
+
 // x <- cap * tanh(x / cap) in place (float32 logits).
 __global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
     pdl_launch_dependents();

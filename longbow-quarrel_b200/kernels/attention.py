@@ -152,22 +152,31 @@ def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None, vd=N
     vd: size of a value head (default hd); sink: float32 [H], one more term of each head's softmax
     denominator; gate: [T, H*vd] whose sigmoid multiplies the output."""
     vd = vd or hd
-    if vd != hd or sink is not None or gate is not None:
+    if vd != hd:
         return general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate)
-    aligned = qkv.stride(0) % 8 == 0
+    out = _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate)
+    if gate is not None and out is not None:
+        return ops.gate_mul(out, gate, "sigmoid")         # the tensor-core kernels leave the gate to a kernel of its own
+    return out if out is not None else general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate)
+
+
+def _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate):
+    """The tensor-core kernels where they take the sizes; None where only the plain kernel does and a gate
+    is to be applied (the plain kernel applies it itself)."""
+    aligned = qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
     if not ctx.decode and aligned:
         kind = prefill_kernel(qkv.dtype, hd, cache_view.page_size)
         if kind == "tc":
             blocks = _blocks(ctx, "query_blocks128")
             if blocks is not None:
                 return ops.attn_prefill_tc(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.slots,
-                                           ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, window)
+                                           ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, window, sink=sink)
             kind = "mma" if "query_blocks64" in ctx.extra else None
         if kind == "mma":
             blocks = _blocks(ctx, "query_blocks64")
             if blocks is not None:
                 return ops.attn_prefill(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.slots,
-                                        ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, window)
+                                        ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, window, sink=sink)
     if ctx.decode and aligned and decode_kernel(qkv.dtype, hd) and cache_view.page_size % 16 == 0:
         work = ctx.extra.get(decode_work_name(H, Hkv, window))
         if work is not None and work.numel():
@@ -175,13 +184,16 @@ def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None, vd=N
             if work.numel() == decode_work_size(ctx.T, teams):
                 return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                        ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window,
-                                       min(MAX_SPLITS, teams), next_w=next_w, early_loads=True, work=work, teams=teams)
+                                       min(MAX_SPLITS, teams), next_w=next_w, early_loads=True, work=work, teams=teams,
+                                       sink=sink)
         n_splits = decode_splits(ctx.T, Hkv, -(-(H // Hkv) // 16), ctx.max_kv, resident_blocks(qkv.device, hd))
         return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits,
-                               next_w=next_w, early_loads=True)      # a decode step: one new token per sequence
+                               next_w=next_w, early_loads=True, sink=sink)      # a decode step: one new token per sequence
+    if gate is not None:
+        return None
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
-                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window)
+                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, sink=sink)
 
 
 def general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate):

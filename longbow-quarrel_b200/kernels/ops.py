@@ -364,6 +364,16 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch.Tensor:
+    """x *= act(gate) in place; x [rows, cols] contiguous, gate a [rows, cols] view whose rows may be strided."""
+    rows, cols = x.shape
+    if gate.dtype != x.dtype or tuple(gate.shape) != (rows, cols) or gate.stride(1) != 1:
+        raise KernelError("gate_mul: the gate must have x's shape and dtype and unit column stride")
+    fn = _fn("plain_kernels", "lq_gate_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(gate), gate.stride(0), dtype_code(x), rows, cols, GATES[act], _stream()), "gate_mul")
+    return x
+
+
 # ------------------------------------------------------------------ mixers with a matrix state per head
 def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, cu_rows, slots, tok_pos,
                 B: int, H: int, dk: int, dv: int, q_scale: float = 1.0, k_scale: float = 1.0,
@@ -674,8 +684,14 @@ def gemm_tc_status() -> int:
     return int(fn())
 
 
+def _check_sink(sink, H: int):
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != H or not sink.is_contiguous()):
+        raise KernelError("attention: sink must be contiguous float32 [H]")
+
+
 def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, query_blocks, H: int, Hkv: int, hd: int,
-                 page_size: int, scale: float, window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+                 page_size: int, scale: float, window: int | None, out: torch.Tensor | None = None,
+                 sink: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of blocks of query rows over the paged bfloat16 cache (flash style:
     tensor-core products, online softmax in float32).  query_blocks = (sequence, first row,
     rows, first position) int32 tensors, one entry for each block of at most 64 rows."""
@@ -689,16 +705,17 @@ def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, q
     qb_seq, qb_row, qb_rows, qb_pos = query_blocks
     fn = _fn("attn_prefill", "lq_attn_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                 c_int, c_int, c_float, c_int, c_void_p])
+                                                 c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check_sink(sink, H)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(slots), _p(kv_len),
               _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos), _p(out), qb_seq.numel(), H, Hkv, hd, page_size,
-              float(scale), int(window or 0), _stream()), "attn_prefill")
+              float(scale), int(window or 0), _p(sink), _stream()), "attn_prefill")
     return out
 
 
 def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, query_blocks128, H: int, Hkv: int,
                     hd: int, page_size: int, scale: float, window: int | None,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor:
     """attn_prefill on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory): blocks of at
     most 128 query rows, head_dim 64 or 128, pages of 64 keys, a cache that is finite everywhere."""
     T = q.shape[0]
@@ -711,10 +728,11 @@ def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len
     qb_seq, qb_row, qb_rows, qb_pos = query_blocks128
     fn = _fn("attn_prefill_tc", "lq_attn_prefill_tc", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+                                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check_sink(sink, H)
     _check(fn(_p(q), q.stride(0), T, _p(_contig(k_pages, "k_pages")), _p(_contig(v_pages, "v_pages")), k_pages.shape[0],
               _p(page_table), page_table.stride(0), _p(slots), _p(kv_len), _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos),
-              _p(out), qb_seq.numel(), H, Hkv, hd, page_size, float(scale), int(window or 0), _stream()), "attn_prefill_tc")
+              _p(out), qb_seq.numel(), H, Hkv, hd, page_size, float(scale), int(window or 0), _p(sink), _stream()), "attn_prefill_tc")
     return out
 
 
@@ -728,7 +746,7 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
                 page_size: int, scale: float, window: int | None, n_splits: int,
                 out: torch.Tensor | None = None, scratch: tuple | None = None,
                 next_w: torch.Tensor | None = None, early_loads: bool = False,
-                work: torch.Tensor | None = None, teams: int = 0) -> torch.Tensor:
+                work: torch.Tensor | None = None, teams: int = 0, sink: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of single query rows over the paged bfloat16 cache, the keys of each
     sequence cut into n_splits slices that are merged afterwards.  With `work` (int32: teams + 1 offsets,
     then (token, first tile, last tile + 1, part, parts) per segment) the grid is `teams` blocks per kv
@@ -764,14 +782,16 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
     if work is not None and (work.dtype != torch.int32 or not work.is_contiguous() or teams < 1
                              or work.numel() < teams + 1 + 5 * T):
         raise KernelError("attn_decode: the work list must be int32 with teams + 1 offsets and at least a segment per token")
-    fn = _fn("attn_decode", "lq_attn_decode_work", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+    _check_sink(sink, H)
+    fn = _fn("attn_decode", "lq_attn_decode_sink", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                     c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int,
-                                                    c_void_p, c_long, c_int, c_void_p])
+                                                    c_void_p, c_long, c_int, c_void_p, c_void_p])
     next_p, next_n = _next(next_w, PREFETCH_BYTES_ATTN)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
-              float(scale), int(window or 0), n_splits, _p(work), int(teams), next_p, next_n, int(early_loads), _stream()),
+              float(scale), int(window or 0), n_splits, _p(work), int(teams), next_p, next_n, int(early_loads), _p(sink),
+              _stream()),
            "attn_decode", 2 if n_splits > 1 and counters is None else 1,
            "attn_decode:teams" if work is not None else "attn_decode:one_slice" if n_splits == 1 else "attn_decode:slices")
     return out

@@ -28,15 +28,23 @@ def _plain(folder, toks):
     return cfg, weights, plain_fetorax.forward(cfg, weights, toks).numpy()
 
 
-def _check(got: dict, requests: dict, folder, dtype: str, what: str, factor: float = 1.0):
+def _check(got: dict, requests: dict, folder, dtype: str, what: str):
+    """float32: every row within its request's bound.  bfloat16: single rows of a request amplify rounding far more
+    than its others (a unit norm of a nearly cancelled sum), so no row may exceed one and a half times the bound
+    and at most one row in fifty the bound itself."""
+    over = total = 0
     for rid, toks in requests.items():
         cfg, weights, ref = _plain(folder, toks)
-        tol = factor * bound(dtype, cfg, weights, toks, ref)
+        tol = bound(dtype, cfg, weights, toks, ref)
         keys = [k for k in got if k[0] == rid]
         assert keys, f"{what}: nothing came back for {rid}"
         for _, pos in keys:
             err = float(row_errors(got[(rid, pos)], ref[pos]))
-            assert err < tol, f"{what}: request {rid} position {pos} of {len(toks)}: error {err:.3g}, bound {tol:.3g}"
+            hard = tol if dtype == "float32" else 1.5 * tol
+            assert err < hard, f"{what}: request {rid} position {pos} of {len(toks)}: error {err:.3g}, bound {hard:.3g}"
+            over += err >= tol
+            total += 1
+    assert over <= 0.02 * total, f"{what}: {over} of {total} rows over their bound"
 
 
 # ------------------------------------------------------------------ each mixer alone
@@ -193,4 +201,26 @@ def test_random_weights_from_a_configuration(tmp_path):
     eng = Engine.from_config(CONFIGS["head64"], seed=3, max_tokens=256, max_batch=2)
     out = eng.generate([[1, 2, 3], [4]], max_new_tokens=5, sampling=SamplingParams(temperature=0.0), stop_ids=[])
     assert [len(o) for o in out] == [5, 5]
+    eng.close()
+
+
+@pytest.mark.parametrize("name,prefill", [("head64", "attn_prefill_tc"), ("mixed", "attn_prefill")])
+def test_the_tensor_core_attention_kernels_serve_the_design(tmp_path, name, prefill):
+    """In bfloat16, attention layers whose values are as wide as their keys run on the kernels that the other
+    models use (tcgen05 prefill at head size 64, mma.sync prefill at 32, split decode), with the sink in their
+    denominators and the gate applied after them: every position of a 300-token prompt and of 20 decoded tokens."""
+    from longbow_quarrel_b200.kernels import ops
+    folder = make_folder(tmp_path, name, seed=61)
+    toks = tokens(320, CONFIGS[name]["vocab"], 62)
+    cfg, weights, ref = _plain(folder, toks)
+    tol = bound("bfloat16", cfg, weights, toks, ref)
+    eng = _engine(folder, "bfloat16", max_tokens=2 * 320)
+    before = ops.launches_by_name()
+    s = eng.new_sequence()
+    rows = [eng.step([(s, toks[:300])], [list(range(300))]).cpu().numpy()]
+    rows += [eng.step([(s, [t])], [[0]]).cpu().numpy() for t in toks[300:]]
+    ran = ops.launches_since(before)
+    assert ran.get(prefill, 0) >= 2 and ran.get("attn_decode", 0) >= 2 * 20 and ran.get("gate_mul", 0) >= 2 * 21, ran
+    errs = row_errors(np.concatenate(rows), ref)
+    assert errs.max() < tol, (int(errs.argmax()), float(errs.max()), tol)
     eng.close()
