@@ -293,8 +293,172 @@ def tiny_workloads(torch) -> dict:
     return out
 
 
+# ------------------------------------------------------------------ --design fetorax: the design beside Llama at equal layer sizes
+DESIGN_SIZES = {   # width, heads, kv heads, head size, feed-forward width: the layer sizes of the 1B and 8B Llama shapes
+    "1b": (2048, 32, 8, 64, 8192),
+    "8b": (4096, 32, 8, 128, 14336),
+}
+DESIGN_VOCAB = 32000
+
+
+def fetorax_config(width, heads, kv_heads, dim, ff, groups: int = 1) -> dict:
+    """`groups` times four layers: attention, retention, mlstm, attention on the first one's keys and values."""
+    rot = {"dims": dim // 2, "base": 1e6, "scaling": {"factor": 2.0}}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = []
+    for g in range(groups):
+        att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot}
+        layers += [
+            {"type": "attention", "mixer": dict(att), "mlp": mlp},
+            {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "rot": {"dims": dim, "base": 1e4},
+                                            "decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)]}, "mlp": mlp},
+            {"type": "mlstm", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "gate_cap": 15.0}, "mlp": mlp},
+            {"type": "attention", "mixer": dict(att, kv_from=4 * g), "mlp": mlp},
+        ]
+    return {"architecture": "Fetorax", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "layers": layers,
+            "logit_softcap": 30.0, "max_positions": 8192}
+
+
+def _kernel_times(torch, run, warm: int = 2) -> tuple[dict, float]:
+    """What every kind of kernel adds to the device time of one call of run(): {kind: (launches, total us)}, and the span."""
+    import re
+
+    from torch.profiler import ProfilerActivity, profile
+    for _ in range(warm):
+        run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and not re.search("[Mm]emcpy|[Mm]emset", e.name)]
+    # Kernels are launched ahead and wait for the one before them, so a kernel's own span overlaps its
+    # predecessor's: what counts is by how much it ends after the kernel before it.
+    ev.sort(key=lambda e: e.time_range.start)
+    kinds: dict = {}
+    prev_end = ev[0].time_range.start if ev else 0.0
+    for e in ev:
+        m = re.search(r"(\w+)_kernel", e.name)
+        k = kinds.setdefault(m.group(1) if m else e.name[:40], [0, 0.0])
+        k[0] += 1
+        k[1] += max(0.0, e.time_range.end - prev_end)
+        prev_end = max(prev_end, e.time_range.end)
+    span = max(e.time_range.end for e in ev) - min(e.time_range.start for e in ev) if ev else 0.0
+    return {k: (n, round(us, 1)) for k, (n, us) in sorted(kinds.items(), key=lambda kv: -kv[1][1])}, round(span, 1)
+
+
+def design_bench(args) -> int:
+    """Prefill and decode of a Fetorax model of the 1B and 8B layer sizes beside a Llama model of the same sizes
+    (random weights, vocabulary cut to 32,000): tokens a second, the device time of every kind of kernel in one
+    prompt step and one decode step, and for the kernels that the design added how many times their roofline
+    they take, beside the like kernel of the Llama model (attention)."""
+    import numpy as np
+    import torch
+
+    from longbow_quarrel_b200.engine import Engine
+    peaks, peaks_from = load_peaks()
+    K, W = args.steps, max(3, args.warmup)
+    T, B, ctx = PREFILL_TOKENS, BATCH, 2048
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size in args.sizes.split(","):
+        width, heads, kv, dim, ff = DESIGN_SIZES[size]
+        configs = {"fetorax": fetorax_config(width, heads, kv, dim, ff),
+                   "llama": dict(llama(width, 4, heads, kv, dim, ff, 8.0, False), vocab_size=DESIGN_VOCAB, max_position_embeddings=8192)}
+        res = {}
+        for name, cfg in configs.items():
+            eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (ctx + 256) + T + 64, max_batch=B + 1,
+                                     max_context=ctx + 256, gain_std=0.0 if name == "llama" else 0.1)
+            prompt = rng.integers(0, DESIGN_VOCAB, T).tolist()
+
+            def prefill():
+                s = eng.new_sequence()
+                eng.step([(s, prompt)])
+                eng.end_sequence(s)
+            for _ in range(W):
+                prefill()
+            a, b = events(torch)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(max(3, K // 4)):
+                prefill()
+            b.record()
+            torch.cuda.synchronize()
+            prefill_ms = a.elapsed_time(b) / max(3, K // 4)
+            prefill_kinds, prefill_span = _kernel_times(torch, prefill)
+            slots = [eng.new_sequence() for _ in range(B)]
+            eng.step([(s, rng.integers(0, DESIGN_VOCAB, ctx).tolist()) for s in slots])
+            feed = rng.integers(0, DESIGN_VOCAB, (W + K + 8, B))
+            at = [0]
+
+            def decode():
+                eng.step([(s, [int(t)]) for s, t in zip(slots, feed[at[0]])])
+                at[0] += 1
+            for _ in range(W):
+                decode()
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(K):
+                decode()
+            b.record()
+            torch.cuda.synchronize()
+            decode_ms = a.elapsed_time(b) / K
+            decode_kinds, decode_span = _kernel_times(torch, decode)
+            res[name] = {"prefill_tokens_per_s": round(T / prefill_ms * 1e3), "prefill_ms": round(prefill_ms, 3),
+                         "decode_tokens_per_s": round(B / decode_ms * 1e3), "decode_ms_per_step": round(decode_ms, 4),
+                         "prefill_kernels_us": prefill_kinds, "decode_kernels_us": decode_kinds,
+                         "weight_bytes": eng.model.weight_bytes()}
+            eng.close()
+            del eng
+            torch.cuda.empty_cache()
+
+        # ---- distance from the roofline, kernel by kernel (us per launch over the us that its bytes or FLOPs take)
+        def per_launch(kinds, *names):
+            n = sum(kinds[k][0] for k in names if k in kinds)
+            return sum(kinds[k][1] for k in names if k in kinds) / n if n else None
+
+        def times(us, nbytes, flops):
+            return round(us / (max(nbytes / hbm, flops / tensor) * 1e6), 2) if us else None
+        f, l = res["fetorax"], res["llama"]
+        qkv_bytes = lambda rows: rows * heads * 3 * dim * 2.0
+        att_flops = 4.0 * heads * dim * T * (T + 1) / 2
+        scan_flops = 4.0 * T * heads * dim * dim
+        state = B * heads * dim * dim * 4.0 * 2
+        kv_read = B * ctx * 2 * kv * dim * 2.0
+        roof = {
+            "prefill": {
+                "llama attention": times(per_launch(l["prefill_kernels_us"], "attn_prefill_two", "attn_prefill_tc", "attn_prefill"),
+                                         qkv_bytes(T), att_flops),
+                "fetorax attention (with sink)": times(per_launch(f["prefill_kernels_us"], "attn_prefill_two", "attn_prefill_tc", "attn_prefill"),
+                                                       qkv_bytes(T), att_flops),
+                "fetorax recurrent scan": times(per_launch(f["prefill_kernels_us"], "linear_scan"),
+                                                qkv_bytes(T) + T * heads * dim * 4.0, scan_flops),
+            },
+            "decode": {
+                "llama attention": times(per_launch(l["decode_kernels_us"], "attn_decode"), kv_read, 0.0),
+                "fetorax attention (with sink)": times(per_launch(f["decode_kernels_us"], "attn_decode"), kv_read, 0.0),
+                "fetorax recurrent scan": times(per_launch(f["decode_kernels_us"], "linear_scan"), state, 0.0),
+            },
+        }
+        out[size] = {"fetorax": f, "llama": l, "times_the_roofline": roof,
+                     "fetorax_over_llama": {"prefill": round(f["prefill_tokens_per_s"] / l["prefill_tokens_per_s"], 3),
+                                            "decode": round(f["decode_tokens_per_s"] / l["decode_tokens_per_s"], 3)}}
+    clocks = sampler.stop()
+    print(json.dumps({"design": "fetorax", "beside": "llama", "dtype": "bf16", "data": "synthetic", "layers": 4,
+                      "layer_order": "attention, retention, mlstm, attention on the first layer's keys and values",
+                      "vocab": DESIGN_VOCAB, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx, "steps": K,
+                      "warmup": W, "peaks": peaks, "peaks_from": peaks_from, "clocks": clocks, "sizes": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default="", choices=["", "fetorax"],
+                    help="instead of the default workload: this design beside Llama at equal layer sizes (prefill, decode, kernel by kernel)")
+    ap.add_argument("--sizes", default="1b,8b", help="--design: layer sizes to run, of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
@@ -306,6 +470,8 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+    if args.design:
+        return design_bench(args)
     if args.gpus != 1:
         print(f"bench.py measures a one-GPU library: --gpus {args.gpus} is not supported, run it with --gpus 1")
         return 2

@@ -514,9 +514,32 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
     if (i < total) out[i] = from_f32<T>(activation(to_f32(x[i]), act));
 }
 
+// Sixteen bytes per thread, where the sizes and addresses allow it.
+template <typename T>
+__global__ void activation_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, size_t pieces, int act) {
+    constexpr int VEC = 16 / sizeof(T);
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= pieces) return;
+    uint4 v = x[i];
+    T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) e[j] = from_f32<T>(activation(to_f32(e[j]), act));
+    out[i] = v;
+}
+
 LQ_EXPORT int lq_activation(const void* x, void* out, int dtype, long long total, int act, cudaStream_t stream) {
     if (total <= 0) return LQ_OK;
     if (act < 0 || act > 3) return LQ_BAD_SIZE;
+    const int vec = dtype == LQ_F32 ? 4 : 8;
+    if ((dtype == LQ_F32 || dtype == LQ_BF16) && total % vec == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const size_t pieces = (size_t)total / vec;
+        const unsigned vblocks = (unsigned)((pieces + 255) / 256);
+        if (dtype == LQ_F32)
+            return launch_pdl(activation_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, (const uint4*)x, (uint4*)out, pieces, act);
+        return launch_pdl(activation_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, (const uint4*)x, (uint4*)out, pieces, act);
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == LQ_F32)
         return launch_pdl(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)total, act);

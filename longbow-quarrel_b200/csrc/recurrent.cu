@@ -15,8 +15,8 @@
 #include "common.cuh"
 #include <math_constants.h>
 
-constexpr int SC_R = 8;          // threads that share one value column (each holds every 8th key row of it)
-constexpr int SC_COLS = 16;      // value columns of a block
+constexpr int SC_R = 32;         // threads that share one value column: a warp, lane r holding key rows r, r + 32, ...
+constexpr int SC_COLS = 16;      // value columns of a block (one warp each)
 constexpr int SC_THREADS = SC_R * SC_COLS;
 constexpr int SC_CHUNK = 16;     // tokens staged in shared memory at a time
 
@@ -43,118 +43,234 @@ struct ScanArgs {
     int H, dk, dv;
 };
 
+// One block walks the tokens of one (sequence, head, 16 value columns) in chunks of SC_CHUNK; a warp owns a column,
+// lane r the key rows r, r + 32, ... of it (KR of them).  While a chunk is multiplied, the next chunk's q, k and v
+// are already on their way from memory into registers; they go to the other of two shared-memory buffers when
+// the chunk is done (then rotated there pair by pair, then scaled).  Within a chunk a lane's share of S advances
+// token by token (its only dependence); the outputs' partial sums stay in registers and are added across the
+// warp once per chunk, in a fixed order.  The block's tile of the state comes and goes through shared memory in
+// whole rows.
 template <typename T, int KR, bool MLSTM>
 __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
-    pdl_wait();
     extern __shared__ float sm[];
-    const int dk = a.dk, dv = a.dv, dvx = dv + (MLSTM ? 1 : 0), H = a.H;
-    float* qs = sm;                              // [CHUNK][dk]
-    float* ks = qs + SC_CHUNK * dk;              // [CHUNK][dk]
-    float* vs = ks + SC_CHUNK * dk;              // [CHUNK][COLS], already times b_t
-    float* as = vs + SC_CHUNK * SC_COLS;         // [CHUNK] a_t
-    float* gi = as + SC_CHUNK;                   // [CHUNK] i_t, then b_t
-    float* gf = gi + SC_CHUNK;                   // [CHUNK] f_t
-    float* ms = gf + SC_CHUNK;                   // [CHUNK + 1] m before each token of the chunk, and after the last
+    const int dk = a.dk, dv = a.dv, dvx = dv + (MLSTM ? 1 : 0), dkx = dk + (MLSTM ? 1 : 0), H = a.H;
+    const int qk_floats = SC_CHUNK * dk;
+    // Two buffers each of q [CHUNK][dk], k [CHUNK][dk] and v [CHUNK][COLS].
+    auto qs = [&](int buf) { return sm + buf * 2 * qk_floats; };
+    auto ks = [&](int buf) { return sm + buf * 2 * qk_floats + qk_floats; };
+    auto vs = [&](int buf) { return sm + 4 * qk_floats + buf * SC_CHUNK * SC_COLS; };
+    float* as2 = sm + 4 * qk_floats + 2 * SC_CHUNK * SC_COLS;     // [2][CHUNK] a_t of the chunk in each buffer
+    float* gi = as2 + 2 * SC_CHUNK;              // [CHUNK] b_t of the chunk being staged
+    float* ms = gi + SC_CHUNK;                   // [CHUNK + 1] the running maximum after the chunk being staged
+    float* tile = ms + SC_CHUNK + 1;             // [dkx][COLS + 1]: the block's columns of the state
     const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SC_COLS;
     const int tid = threadIdx.x, c = tid / SC_R, rr = tid % SC_R, col = col0 + c;
-    const bool live = col < dvx;
+    const int n_cols = min(SC_COLS, dvx - col0);
+    const bool live = c < n_cols;
+    const T* base = (const T*)a.qkv;
+    const int half = a.rot >> 1;
+    constexpr int RF = (KR + 1) / 2;             // a thread's share of a chunk's rotated pairs
+    pdl_wait();
     const int row0 = a.cu_rows[b], row1 = a.cu_rows[b + 1];
-    float* st = a.state + (long long)a.slots[b] * a.slot_stride + (size_t)h * (dk + (MLSTM ? 1 : 0)) * dvx;
+    float* st = a.state + (long long)a.slots[b] * a.slot_stride + (size_t)h * dkx * dvx + col0;
+    for (int e = tid; e < dkx * SC_COLS; e += SC_THREADS) {
+        const int r = e / SC_COLS, cc = e % SC_COLS;
+        tile[r * (SC_COLS + 1) + cc] = cc < n_cols ? st[(size_t)r * dvx + cc] : 0.f;
+    }
+    __syncthreads();
     float S[KR];
 #pragma unroll
     for (int i = 0; i < KR; ++i) {
         const int r = i * SC_R + rr;
-        S[i] = (live && r < dk) ? st[(size_t)r * dvx + col] : 0.f;
+        S[i] = r < dk ? tile[r * (SC_COLS + 1) + c] : 0.f;
     }
     float m = 0.f;
-    if (MLSTM) m = st[(size_t)dk * dvx + (live ? col : col0)];
+    if (MLSTM) m = tile[dk * (SC_COLS + 1)];
     const float decay = MLSTM ? 0.f : a.decay[h];
-    const T* base = (const T*)a.qkv;
-    const int half = a.rot >> 1;
 
-    for (int t0 = row0; t0 < row1; t0 += SC_CHUNK) {
-        const int n = min(SC_CHUNK, row1 - t0);
-        // ---- stage q and k (rotated, scaled) and this block's value columns
-        for (int e = tid; e < n * dk; e += SC_THREADS) {
-            const int t = e / dk, j = e % dk;
-            const T* row = base + (size_t)(t0 + t) * a.stride;
-            const T* qh = row + a.q_off + h * dk;
-            const T* kh = row + a.k_off + h * dk;
-            float qv = to_f32(qh[j]), kv = to_f32(kh[j]);
-            if (j < a.rot) {
-                const int f = j < half ? j : j - half, jp = j < half ? j + half : j - half;
-                const size_t at = (size_t)a.tok_pos[t0 + t] * half + f;
-                const float cs = a.cos_t[at], sn = j < half ? -a.sin_t[at] : a.sin_t[at];
-                qv = qv * cs + to_f32(qh[jp]) * sn;
-                kv = kv * cs + to_f32(kh[jp]) * sn;
-            }
-            qs[t * dk + j] = qv * a.q_scale;
-            ks[t * dk + j] = kv * a.k_scale;
-        }
-        if (MLSTM) {
-            if (tid < n) {
-                const float* g = a.gate_pre + (size_t)(t0 + tid) * 2 * H;
-                const float cap = a.gate_cap;
-                gi[tid] = cap * tanhf((g[h] + a.gate_bias[h]) / cap);
-                gf[tid] = log_sigmoid(cap * tanhf((g[H + h] + a.gate_bias[H + h]) / cap));
-            }
-            __syncthreads();
-            if (tid == 0) {
-                float mm = m;
-                for (int t = 0; t < n; ++t) {
-                    ms[t] = mm;
-                    mm = fmaxf(gf[t] + mm, gi[t]);
-                }
-                ms[n] = mm;
-            }
-            __syncthreads();
-            m = ms[n];
-            if (tid < n) {
-                const float m_new = ms[tid + 1];
-                as[tid] = expf(gf[tid] + ms[tid] - m_new);
-                gi[tid] = expf(gi[tid] - m_new);
-                if (blockIdx.z == 0) a.exp_neg_m[(size_t)(t0 + tid) * H + h] = expf(-m_new);
-            }
-            __syncthreads();
-        }
-        for (int e = tid; e < n * SC_COLS; e += SC_THREADS) {
-            const int t = e / SC_COLS, cc = e % SC_COLS, vc = col0 + cc;
-            float v = 0.f;
-            if (vc < dv) v = to_f32(base[(size_t)(t0 + t) * a.stride + a.v_off + h * dv + vc]);
-            else if (MLSTM && vc == dv) v = 1.f;
-            vs[e] = MLSTM ? v * gi[t] : v;
-        }
-        __syncthreads();
-        // ---- the recurrence, token by token
-        for (int t = 0; t < n; ++t) {
-            const float at = MLSTM ? as[t] : decay;
-            const float bv = vs[t * SC_COLS + c];
-            const float* kt = ks + t * dk;
-            const float* qt = qs + t * dk;
-            float acc = 0.f;
+    float q_pf[KR], k_pf[KR], cs_pf[RF], sn_pf[RF], v_pf = 0.f, gi_pf = 0.f, gf_pf = 0.f;
+    // Element e of a chunk's q (k) is token e / dk, dimension e % dk; thread tid holds e = tid + i * THREADS.
+    // Which token and which place that is does not change from chunk to chunk: worked out once.
+    int e_tok[KR], e_off[KR], r_tok[RF], r_dim[RF];
 #pragma unroll
-            for (int i = 0; i < KR; ++i) {
-                const int r = i * SC_R + rr;
-                if (r < dk) {
-                    S[i] = fmaf(at, S[i], bv * kt[r]);
-                    acc = fmaf(S[i], qt[r], acc);
-                }
-            }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (rr == 0 && live) a.out[((size_t)(t0 + t) * H + h) * dvx + col] = acc;
-        }
-        __syncthreads();
+    for (int i = 0; i < KR; ++i) {
+        const int e = tid + i * SC_THREADS;
+        e_tok[i] = e / dk;                                            // >= CHUNK beyond the chunk
+        e_off[i] = e_tok[i] * a.stride + h * dk + e % dk;
     }
-    if (live) {
+#pragma unroll
+    for (int i = 0; i < RF; ++i) {
+        const int e = tid + i * SC_THREADS;
+        r_tok[i] = half ? e / half : SC_CHUNK;
+        r_dim[i] = half ? e % half : 0;
+    }
+    const int v_tok = tid / SC_COLS, v_col = col0 + tid % SC_COLS;
+    const int v_at = v_tok * a.stride + a.v_off + h * dv + v_col;
+    auto fetch = [&](int t0) {
+        const int n = min(SC_CHUNK, row1 - t0);
+        const T* rows = base + (size_t)t0 * a.stride;
 #pragma unroll
         for (int i = 0; i < KR; ++i) {
-            const int r = i * SC_R + rr;
-            if (r < dk) st[(size_t)r * dvx + col] = S[i];
+            q_pf[i] = k_pf[i] = 0.f;
+            if (e_tok[i] < n) {
+                q_pf[i] = to_f32(rows[e_off[i] + a.q_off]);
+                k_pf[i] = to_f32(rows[e_off[i] + a.k_off]);
+            }
         }
-        if (MLSTM && rr == 0) st[(size_t)dk * dvx + col] = m;
+        if (half) {
+#pragma unroll
+            for (int i = 0; i < RF; ++i) {
+                cs_pf[i] = 1.f;
+                sn_pf[i] = 0.f;
+                if (r_tok[i] < n) {
+                    const size_t at = (size_t)a.tok_pos[t0 + r_tok[i]] * half + r_dim[i];
+                    cs_pf[i] = a.cos_t[at];
+                    sn_pf[i] = a.sin_t[at];
+                }
+            }
+        }
+        if (v_tok < SC_CHUNK) {
+            v_pf = 0.f;
+            if (v_tok < n) {
+                if (v_col < dv) v_pf = to_f32(rows[v_at]);
+                else if (MLSTM && v_col == dv) v_pf = 1.f;
+            }
+        }
+        if (MLSTM && tid < n) {
+            const float* g = a.gate_pre + (size_t)(t0 + tid) * 2 * H;
+            gi_pf = g[h] + a.gate_bias[h];
+            gf_pf = g[H + h] + a.gate_bias[H + h];
+        }
+    };
+    // What was fetched goes to buffer `buf`, ready for the recurrence: rotated, scaled, the gates worked out.
+    auto stage = [&](int t0, int buf) {
+        const int n = min(SC_CHUNK, row1 - t0);
+#pragma unroll
+        for (int i = 0; i < KR; ++i) {
+            if (e_tok[i] < n) {
+                qs(buf)[tid + i * SC_THREADS] = q_pf[i];
+                ks(buf)[tid + i * SC_THREADS] = k_pf[i];
+            }
+        }
+        if (MLSTM && tid < 32) {
+            // The gates of the chunk's tokens, one lane each, and the running maximum
+            //   m_t = max(f_t + m_(t-1), i_t) = F_t + max(m_0, max_(s<=t)(i_s - F_s)),  F_t = f_1 + ... + f_t,
+            // as a prefix sum and a prefix maximum over the lanes.  Whatever rounding m_t has, a_t, b_t and
+            // exp(-m_t) are made from the same m_t, so state and normaliser stay scaled alike.
+            const float cap = a.gate_cap;
+            const bool in = tid < n;
+            const float li = in ? cap * tanhf(gi_pf / cap) : -CUDART_INF_F;
+            const float lf = in ? log_sigmoid(cap * tanhf(gf_pf / cap)) : 0.f;
+            float F = lf;
+#pragma unroll
+            for (int o = 1; o < SC_CHUNK; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, F, o);
+                if (tid >= o) F += up;
+            }
+            float g = li - F;
+#pragma unroll
+            for (int o = 1; o < SC_CHUNK; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, g, o);
+                if (tid >= o) g = fmaxf(g, up);
+            }
+            const float m_new = F + fmaxf(m, g);
+            float m_old = __shfl_up_sync(0xffffffffu, m_new, 1);
+            if (tid == 0) m_old = m;
+            if (in) {
+                as2[buf * SC_CHUNK + tid] = expf(lf + m_old - m_new);
+                gi[tid] = expf(li - m_new);
+                if (blockIdx.z == 0) a.exp_neg_m[(size_t)(t0 + tid) * H + h] = expf(-m_new);
+            }
+            if (tid == n - 1) ms[0] = m_new;
+        }
+        __syncthreads();
+        if (MLSTM) m = ms[0];
+        if (half) {
+#pragma unroll
+            for (int i = 0; i < RF; ++i) {
+                if (r_tok[i] < n) {
+                    const int t = r_tok[i], f = r_dim[i];
+                    const float cs = cs_pf[i], sn = sn_pf[i];
+                    float* qp = qs(buf) + t * dk + f;
+                    float* kp = ks(buf) + t * dk + f;
+                    const float qu = qp[0], qw = qp[half], ku = kp[0], kw = kp[half];
+                    qp[0] = qu * cs - qw * sn;
+                    qp[half] = qw * cs + qu * sn;
+                    kp[0] = ku * cs - kw * sn;
+                    kp[half] = kw * cs + ku * sn;
+                }
+            }
+        }
+        __syncthreads();
+        if (v_tok < n) vs(buf)[tid] = MLSTM ? v_pf * gi[v_tok] : v_pf;
+#pragma unroll
+        for (int i = 0; i < KR; ++i) {                              // the scales come after the rotation
+            if (e_tok[i] < n) {
+                qs(buf)[tid + i * SC_THREADS] *= a.q_scale;
+                ks(buf)[tid + i * SC_THREADS] *= a.k_scale;
+            }
+        }
+        __syncthreads();
+    };
+
+    if (row0 < row1) {
+        fetch(row0);
+        stage(row0, 0);
+    }
+    int buf = 0;
+    for (int t0 = row0; t0 < row1; t0 += SC_CHUNK, buf ^= 1) {
+        const int n = min(SC_CHUNK, row1 - t0);
+        const bool more = t0 + SC_CHUNK < row1;
+        if (more) fetch(t0 + SC_CHUNK);          // in flight while this chunk is multiplied
+        float acc[SC_CHUNK];
+#pragma unroll
+        for (int t = 0; t < SC_CHUNK; ++t) {
+            acc[t] = 0.f;
+            if (t < n) {
+                const float at = MLSTM ? as2[buf * SC_CHUNK + t] : decay;
+                const float bv = vs(buf)[t * SC_COLS + c];
+                const float* kt = ks(buf) + t * dk;
+                const float* qt = qs(buf) + t * dk;
+#pragma unroll
+                for (int i = 0; i < KR; ++i) {
+                    const int r = i * SC_R + rr;
+                    if (r < dk) {
+                        S[i] = fmaf(at, S[i], bv * kt[r]);
+                        acc[t] = fmaf(S[i], qt[r], acc[t]);
+                    }
+                }
+            }
+        }
+        // Sixteen sums over the warp's lanes at once: in each of four steps a lane hands half of its values to
+        // the lane across and adds the half it keeps, so that lane l is left with token (l & 15)'s sum over the
+        // lanes that agree with it in bit 4; one more exchange adds the two halves of the warp.
+#pragma unroll
+        for (int w = 8; w >= 1; w >>= 1) {
+            const bool upper = rr & w;
+#pragma unroll
+            for (int t = 0; t < w; ++t) {
+                const float give = upper ? acc[t] : acc[t + w];
+                const float keep = upper ? acc[t + w] : acc[t];
+                acc[t] = keep + __shfl_xor_sync(0xffffffffu, give, w);
+            }
+        }
+        const float mine = acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 16);
+        const int my_tok = rr & 15;              // bits 3..0 of the lane chose the upper or lower half at w = 8, 4, 2, 1
+        if (live && rr < 16 && my_tok < n) a.out[((size_t)(t0 + my_tok) * H + h) * dvx + col] = mine;
+        if (more) stage(t0 + SC_CHUNK, buf ^ 1);
+        else __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < KR; ++i) {
+        const int r = i * SC_R + rr;
+        if (r < dk) tile[r * (SC_COLS + 1) + c] = S[i];
+    }
+    if (MLSTM && rr == 0) tile[dk * (SC_COLS + 1) + c] = m;
+    __syncthreads();
+    for (int e = tid; e < dkx * SC_COLS; e += SC_THREADS) {
+        const int r = e / SC_COLS, cc = e % SC_COLS;
+        if (cc < n_cols) st[(size_t)r * dvx + cc] = tile[r * (SC_COLS + 1) + cc];
     }
 }
 
@@ -162,10 +278,18 @@ template <typename T, bool MLSTM>
 static int scan_launch(const ScanArgs& a, int B, cudaStream_t stream) {
     const int dvx = a.dv + (MLSTM ? 1 : 0);
     dim3 grid(B, a.H, (dvx + SC_COLS - 1) / SC_COLS);
-    size_t smem = (size_t)(2 * SC_CHUNK * a.dk + SC_CHUNK * SC_COLS + 4 * SC_CHUNK + 1) * sizeof(float);
-    if (a.dk <= 8 * SC_R) return launch_pdl(linear_scan_kernel<T, 8, MLSTM>, grid, dim3(SC_THREADS), smem, stream, a);
-    if (a.dk <= 16 * SC_R) return launch_pdl(linear_scan_kernel<T, 16, MLSTM>, grid, dim3(SC_THREADS), smem, stream, a);
-    if (a.dk <= 32 * SC_R) return launch_pdl(linear_scan_kernel<T, 32, MLSTM>, grid, dim3(SC_THREADS), smem, stream, a);
+    const size_t smem = (size_t)(4 * SC_CHUNK * a.dk + 2 * SC_CHUNK * SC_COLS + 4 * SC_CHUNK + 1 +
+                                 (a.dk + 1) * (SC_COLS + 1)) * sizeof(float);      // a little more than the kernel lays out
+    auto go = [&](auto kernel) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return lq_launch_status();
+        return launch_pdl(kernel, grid, dim3(SC_THREADS), smem, stream, a);
+    };
+    if (a.dk <= 1 * SC_R) return go(linear_scan_kernel<T, 1, MLSTM>);
+    if (a.dk <= 2 * SC_R) return go(linear_scan_kernel<T, 2, MLSTM>);
+    if (a.dk <= 4 * SC_R) return go(linear_scan_kernel<T, 4, MLSTM>);
+    if (a.dk <= 8 * SC_R) return go(linear_scan_kernel<T, 8, MLSTM>);
     return LQ_BAD_SIZE;
 }
 
@@ -237,5 +361,67 @@ LQ_EXPORT int lq_head_norm_gate(const float* raw, int dvx, const float* exp_neg_
     if (dtype == LQ_BF16)
         return launch_pdl(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, raw, dvx, exp_neg_m, weight,
                           (const __nv_bfloat16*)gate, gate_stride, act, (__nv_bfloat16*)out, n, H, dv, eps);
+    return LQ_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ a projection onto few outputs, in 32-bit
+// out[t, j] = sum_k x[t, k] W[j, k] in float32 for a weight of few rows (the gates of a recurrent mixer: two per
+// head).  One block per four rows of x (kept in shared memory as float32); a warp per output at a time, its lanes
+// striding over k, partial sums added across the lanes in a fixed order: the order of sums depends on K alone.
+constexpr int SP_ROWS = 4;       // rows of x per block: a row of W is read once for all of them
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256) small_proj_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
+                                                         float* __restrict__ out, int rows, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float xs[];                 // [SP_ROWS][K]
+    const int t0 = blockIdx.x * SP_ROWS, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = min(SP_ROWS, rows - t0);
+    for (int e = threadIdx.x; e < SP_ROWS * K; e += 256) xs[e] = e < n * K ? to_f32(x[(size_t)t0 * K + e]) : 0.f;
+    __syncthreads();
+    for (int j = warp; j < N; j += 8) {
+        const TW* wr = w + (size_t)j * K;
+        float s[SP_ROWS][4] = {};
+        int k = lane;
+        for (; k + 96 < K; k += 128) {
+            const float w0 = to_f32(wr[k]), w1 = to_f32(wr[k + 32]), w2 = to_f32(wr[k + 64]), w3 = to_f32(wr[k + 96]);
+#pragma unroll
+            for (int r = 0; r < SP_ROWS; ++r) {
+                const float* xr = xs + r * K + k;
+                s[r][0] = fmaf(xr[0], w0, s[r][0]);
+                s[r][1] = fmaf(xr[32], w1, s[r][1]);
+                s[r][2] = fmaf(xr[64], w2, s[r][2]);
+                s[r][3] = fmaf(xr[96], w3, s[r][3]);
+            }
+        }
+        for (; k < K; k += 32) {
+            const float w0 = to_f32(wr[k]);
+#pragma unroll
+            for (int r = 0; r < SP_ROWS; ++r) s[r][0] = fmaf(xs[r * K + k], w0, s[r][0]);
+        }
+#pragma unroll
+        for (int r = 0; r < SP_ROWS; ++r) {
+            const float v = warp_sum((s[r][0] + s[r][1]) + (s[r][2] + s[r][3]));
+            if (lane == 0 && r < n) out[(size_t)(t0 + r) * N + j] = v;
+        }
+    }
+}
+
+LQ_EXPORT int lq_small_proj(const void* x, int x_dtype, const void* w, int w_dtype, float* out, int rows, int N, int K,
+                            cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return LQ_OK;
+    const size_t smem = (size_t)SP_ROWS * K * sizeof(float);
+    if (smem > 200 * 1024) return LQ_BAD_SIZE;
+    auto go = [&](auto kernel, auto xp, auto wp) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return lq_launch_status();
+        return launch_pdl(kernel, dim3((rows + SP_ROWS - 1) / SP_ROWS), dim3(256), smem, stream, xp, wp, out, rows, N, K);
+    };
+    typedef __nv_bfloat16 bf;
+    if (x_dtype == LQ_F32 && w_dtype == LQ_F32) return go(small_proj_kernel<float, float>, (const float*)x, (const float*)w);
+    if (x_dtype == LQ_F32 && w_dtype == LQ_BF16) return go(small_proj_kernel<float, bf>, (const float*)x, (const bf*)w);
+    if (x_dtype == LQ_BF16 && w_dtype == LQ_F32) return go(small_proj_kernel<bf, float>, (const bf*)x, (const float*)w);
+    if (x_dtype == LQ_BF16 && w_dtype == LQ_BF16) return go(small_proj_kernel<bf, bf>, (const bf*)x, (const bf*)w);
     return LQ_BAD_DTYPE;
 }

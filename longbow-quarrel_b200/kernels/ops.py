@@ -415,6 +415,19 @@ def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
     return out, enm
 
 
+def small_proj(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [rows, K] . w [N, K]^T in float32 for a weight of few rows (gates): every product and sum in 32-bit,
+    the order of sums fixed by K alone."""
+    rows, K = x.shape
+    if w.shape[1] != K:
+        raise KernelError(f"small_proj: input width {K} does not match weight width {w.shape[1]}")
+    out = torch.empty((rows, w.shape[0]), dtype=torch.float32, device=x.device)
+    fn = _fn("recurrent", "lq_small_proj", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(x, "x")), dtype_code(x), _p(_contig(w, "w")), dtype_code(w), _p(out), rows, w.shape[0], K, _stream()),
+           "small_proj")
+    return out
+
+
 GATES = {None: 0, "sigmoid": 1, "silu": 2}
 
 

@@ -133,7 +133,7 @@ class MLSTM(_MatrixStateMixer):
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
         H, dk, dv = self.H, self.dk, self.dv
         rows = linear.linear(h, self.w_in, self.runtime.act_dtype)
-        pre = ops.gemm_plain(h, self.w_gates, torch.float32)        # the gates enter the recurrence: a 32-bit product
+        pre = ops.small_proj(h, self.w_gates)         # the gates enter the recurrence: a 32-bit product of their own
         raw, enm = ops.linear_scan(rows, 0, H * dk, 2 * H * dk, cache_view, ctx.cu_rows, ctx.slots, ctx.tok_pos, ctx.B,
                                    H, dk, dv, q_scale=dk ** -0.5, gates=(pre, self.b_gates, self.cap))
         g_off = 2 * H * dk + H * dv

@@ -298,3 +298,18 @@ def test_activations_and_soft_cap():
     z = torch.linspace(-200, 200, 777).reshape(7, 111).contiguous()
     got = ops.softcap(z.clone().to(DEV), 30.0).cpu().double()
     assert float((got - 30.0 * torch.tanh(z.double() / 30.0)).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("rows,N,K", [(1, 2, 48), (9, 6, 100), (300, 64, 2048), (5, 8, 4100)])
+def test_a_projection_onto_few_outputs_in_32_bit(rows, N, K):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(K)
+    x, w = torch.randn(rows, K, generator=gen), torch.randn(N, K, generator=gen)
+    for xt, wt in ((torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16)):
+        xs, ws = x.to(xt), w.to(wt)
+        got = ops.small_proj(xs.to(DEV), ws.to(DEV)).cpu().double()
+        want = xs.double() @ ws.double().T
+        assert float((got - want).abs().max()) < 2e-6 * K ** 0.5 * float(want.abs().max())
+    # a row's result does not depend on the rows beside it
+    alone = ops.small_proj(x[:1].contiguous().to(DEV), w.to(DEV))
+    assert torch.equal(alone[0], ops.small_proj(x.to(DEV), w.to(DEV))[0])
