@@ -73,22 +73,7 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
     constexpr int RF = (KR + 1) / 2;             // a thread's share of a chunk's rotated pairs
     pdl_wait();
     const int row0 = a.cu_rows[b], row1 = a.cu_rows[b + 1];
-    float* st = a.state + (long long)a.slots[b] * a.slot_stride + (size_t)h * dkx * dvx + col0;
-    for (int e = tid; e < dkx * SC_COLS; e += SC_THREADS) {
-        const int r = e / SC_COLS, cc = e % SC_COLS;
-        tile[r * (SC_COLS + 1) + cc] = cc < n_cols ? st[(size_t)r * dvx + cc] : 0.f;
-    }
-    __syncthreads();
-    float S[KR];
-#pragma unroll
-    for (int i = 0; i < KR; ++i) {
-        const int r = i * SC_R + rr;
-        S[i] = r < dk ? tile[r * (SC_COLS + 1) + c] : 0.f;
-    }
     float m = 0.f;
-    if (MLSTM) m = tile[dk * (SC_COLS + 1)];
-    const float decay = MLSTM ? 0.f : a.decay[h];
-
     float q_pf[KR], k_pf[KR], cs_pf[RF], sn_pf[RF], v_pf = 0.f, gi_pf = 0.f, gf_pf = 0.f;
     // Element e of a chunk's q (k) is token e / dk, dimension e % dk; thread tid holds e = tid + i * THREADS.
     // Which token and which place that is does not change from chunk to chunk: worked out once.
@@ -214,10 +199,23 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
         __syncthreads();
     };
 
-    if (row0 < row1) {
-        fetch(row0);
-        stage(row0, 0);
+    if (row0 < row1) fetch(row0);                // on its way while the state's tile arrives
+    float* st = a.state + (long long)a.slots[b] * a.slot_stride + (size_t)h * dkx * dvx + col0;
+    for (int e = tid; e < dkx * SC_COLS; e += SC_THREADS) {
+        const int r = e / SC_COLS, cc = e % SC_COLS;
+        tile[r * (SC_COLS + 1) + cc] = cc < n_cols ? st[(size_t)r * dvx + cc] : 0.f;
     }
+    __syncthreads();
+    float S[KR];
+#pragma unroll
+    for (int i = 0; i < KR; ++i) {
+        const int r = i * SC_R + rr;
+        S[i] = r < dk ? tile[r * (SC_COLS + 1) + c] : 0.f;
+    }
+    if (MLSTM) m = tile[dk * (SC_COLS + 1)];
+    const float decay = MLSTM ? 0.f : a.decay[h];
+
+    if (row0 < row1) stage(row0, 0);
     int buf = 0;
     for (int t0 = row0; t0 < row1; t0 += SC_CHUNK, buf ^= 1) {
         const int n = min(SC_CHUNK, row1 - t0);
@@ -366,7 +364,7 @@ LQ_EXPORT int lq_head_norm_gate(const float* raw, int dvx, const float* exp_neg_
 
 // ------------------------------------------------------------------ a projection onto few outputs, in 32-bit
 // out[t, j] = sum_k x[t, k] W[j, k] in float32 for a weight of few rows (the gates of a recurrent mixer: two per
-// head).  One block per four rows of x (kept in shared memory as float32); a warp per output at a time, its lanes
+// head).  One block per four rows of x (kept in shared memory as float32) and eight outputs, a warp per output, its lanes
 // striding over k, partial sums added across the lanes in a fixed order: the order of sums depends on K alone.
 constexpr int SP_ROWS = 4;       // rows of x per block: a row of W is read once for all of them
 template <typename TX, typename TW>
@@ -379,7 +377,9 @@ __global__ void __launch_bounds__(256) small_proj_kernel(const TX* __restrict__ 
     const int n = min(SP_ROWS, rows - t0);
     for (int e = threadIdx.x; e < SP_ROWS * K; e += 256) xs[e] = e < n * K ? to_f32(x[(size_t)t0 * K + e]) : 0.f;
     __syncthreads();
-    for (int j = warp; j < N; j += 8) {
+    {
+        const int j = blockIdx.y * 8 + warp;       // a warp per output
+        if (j >= N) return;
         const TW* wr = w + (size_t)j * K;
         float s[SP_ROWS][4] = {};
         int k = lane;
@@ -416,7 +416,7 @@ LQ_EXPORT int lq_small_proj(const void* x, int x_dtype, const void* w, int w_dty
         if (smem > 48 * 1024 &&
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return lq_launch_status();
-        return launch_pdl(kernel, dim3((rows + SP_ROWS - 1) / SP_ROWS), dim3(256), smem, stream, xp, wp, out, rows, N, K);
+        return launch_pdl(kernel, dim3((rows + SP_ROWS - 1) / SP_ROWS, (N + 7) / 8), dim3(256), smem, stream, xp, wp, out, rows, N, K);
     };
     typedef __nv_bfloat16 bf;
     if (x_dtype == LQ_F32 && w_dtype == LQ_F32) return go(small_proj_kernel<float, float>, (const float*)x, (const float*)w);
