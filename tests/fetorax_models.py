@@ -72,6 +72,13 @@ CONFIGS = {
         mlstm(2, 64, 64, 10.0, ff=192),
         attention(4, 2, 64, 64, rot={"dims": 32, "base": 1e6, "scaling": {"factor": 2.0}}, scale=0.125, kv_from=0, ff=192),
     ], softcap=30.0),
+    # head size 128 with three heads on one kv head, and head size 64 with a kv head for every head: the groups
+    # of odd size, which the tensor-core prompt kernel serves one head per block
+    "odd_groups": model(128, 210, [
+        attention(3, 1, 128, 128, rot={"dims": 64, "base": 5e5, "scaling": {"factor": 8.0}}, scale=0.09, ff=160),
+        attention(2, 2, 64, 64, rot={"dims": 64, "base": 1e4}, scale=0.11),
+        attention(3, 1, 128, 128, rot={"dims": 64, "base": 5e5, "scaling": {"factor": 8.0}}, scale=0.2, kv_from=0, ff=96),
+    ], eps=1e-5, softcap=25.0),
     # one layer of each mixer alone, without feed-forward
     "only_attention": model(48, 90, [attention(4, 1, 16, 24, rot={"dims": 16, "base": 100.0, "scaling": {"factor": 1.5}}, scale=0.4)]),
     "only_retention": model(48, 90, [retention(3, 16, 8, [0.8, 0.95, 0.999], rot={"dims": 4, "base": 50.0})]),
