@@ -427,20 +427,23 @@ LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const f
 // Rows of `buf` [T, stride] hold n_rot heads of size hd side by side from column 0 (queries, then keys where
 // the layer has keys of its own), and from column v_off Hkv value heads of size vd.  Each of the n_rot heads
 // gets its bias (bias[column], optional) and has its first `rot` dimensions rotated in pairs (i, i + rot/2)
-// by the angle of its row's position (cos/sin tables [positions, rot/2]); the rest of the head passes.  The
-// result is written back in place.  With a cache, heads k_first.. are also stored into the row's page of
-// k_pages [page][Hkv][page_size][hd], and the values (with their bias) into v_pages [..][vd].
-template <typename T>
+// by the angle of its row's position (cos/sin tables [positions, rot/2]); the rest of the head passes.
+// Heads below k_first (the queries) go to qout [T, qout_stride], which may be buf itself; with a cache, heads
+// k_first.. go into the row's page of k_pages [page][Hkv][page_size][hd], and the values (with their bias)
+// into v_pages [..][vd].  The rows may be float32 while queries and cache are bfloat16: a product's 32-bit sums
+// then meet their biases and angles before anything is rounded.
+template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
-rope_partial_kernel(T* __restrict__ buf, int stride, const float* __restrict__ bias, const float* __restrict__ cos_t,
-                    const float* __restrict__ sin_t, int rot, const int* __restrict__ tok_pos,
-                    const int* __restrict__ tok_seq, const int* __restrict__ slots, const int* __restrict__ page_table,
-                    int pt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_rot, int k_first, int Hkv,
-                    int hd, int vd, int v_off, int page_size) {
+rope_partial_kernel(const TI* buf, int stride, TO* qout, int qout_stride, const float* __restrict__ bias,
+                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+                    const int* __restrict__ page_table, int pt_stride, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
+                    int n_rot, int k_first, int Hkv, int hd, int vd, int v_off, int page_size) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
-    T* row = buf + (size_t)t * stride;
+    const TI* row = buf + (size_t)t * stride;
+    TO* qrow = qout + (size_t)t * qout_stride;
     const float* cs = rot ? cos_t + (size_t)pos * half : nullptr;
     const float* sn = rot ? sin_t + (size_t)pos * half : nullptr;
     size_t at = 0;
@@ -451,47 +454,48 @@ rope_partial_kernel(T* __restrict__ buf, int stride, const float* __restrict__ b
     const int per_head = hd - half;                 // a rotated pair is one piece of work, every other dimension one
     for (int i = threadIdx.x; i < n_rot * per_head; i += 256) {
         const int head = i / per_head, j = i % per_head;
-        T* p = row + (size_t)head * hd;
+        const TI* p = row + (size_t)head * hd;
         const float* b = bias ? bias + (size_t)head * hd : nullptr;
-        T* kd = (k_pages && head >= k_first) ? k_pages + (at + (size_t)(head - k_first) * page_size) * hd : nullptr;
+        TO* qd = head < k_first ? qrow + (size_t)head * hd : nullptr;
+        TO* kd = (k_pages && head >= k_first) ? k_pages + (at + (size_t)(head - k_first) * page_size) * hd : nullptr;
         if (j < half) {
             const float u = to_f32(p[j]) + (b ? b[j] : 0.f), w = to_f32(p[j + half]) + (b ? b[j + half] : 0.f);
             const float c = cs[j], s = sn[j];
-            const T o0 = from_f32<T>(u * c - w * s), o1 = from_f32<T>(w * c + u * s);
-            p[j] = o0;
-            p[j + half] = o1;
+            const TO o0 = from_f32<TO>(u * c - w * s), o1 = from_f32<TO>(w * c + u * s);
+            if (qd) { qd[j] = o0; qd[j + half] = o1; }
             if (kd) { kd[j] = o0; kd[j + half] = o1; }
         } else {
             const int d = j + half;
-            const T o = from_f32<T>(to_f32(p[d]) + (b ? b[d] : 0.f));
-            p[d] = o;
+            const TO o = from_f32<TO>(to_f32(p[d]) + (b ? b[d] : 0.f));
+            if (qd) qd[d] = o;
             if (kd) kd[d] = o;
         }
     }
     if (v_pages) {
-        const T* vsrc = row + v_off;
+        const TI* vsrc = row + v_off;
         const float* b = bias ? bias + v_off : nullptr;
         for (int i = threadIdx.x; i < Hkv * vd; i += 256) {
             const int head = i / vd, j = i % vd;
-            v_pages[(at + (size_t)head * page_size) * vd + j] = from_f32<T>(to_f32(vsrc[i]) + (b ? b[i] : 0.f));
+            v_pages[(at + (size_t)head * page_size) * vd + j] = from_f32<TO>(to_f32(vsrc[i]) + (b ? b[i] : 0.f));
         }
     }
 }
 
-LQ_EXPORT int lq_rope_partial(void* buf, int dtype, int stride, const float* bias, const float* cos_t, const float* sin_t,
-                              int rot, const int* tok_pos, const int* tok_seq, const int* slots, const int* page_table,
-                              int pt_stride, void* k_pages, void* v_pages, int T, int n_rot, int k_first, int Hkv, int hd,
-                              int vd, int v_off, int page_size, cudaStream_t stream) {
+LQ_EXPORT int lq_rope_partial(const void* buf, int in_dtype, int stride, void* qout, int out_dtype, int qout_stride,
+                              const float* bias, const float* cos_t, const float* sin_t, int rot, const int* tok_pos,
+                              const int* tok_seq, const int* slots, const int* page_table, int pt_stride, void* k_pages,
+                              void* v_pages, int T, int n_rot, int k_first, int Hkv, int hd, int vd, int v_off,
+                              int page_size, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (rot % 2 || rot > hd || (rot && (!cos_t || !sin_t)) || (!k_pages) != (!v_pages)) return LQ_BAD_SIZE;
-    if (dtype == LQ_F32)
-        return launch_pdl(rope_partial_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)buf, stride, bias, cos_t, sin_t,
-                          rot, tok_pos, tok_seq, slots, page_table, pt_stride, (float*)k_pages, (float*)v_pages, n_rot,
-                          k_first, Hkv, hd, vd, v_off, page_size);
-    if (dtype == LQ_BF16)
-        return launch_pdl(rope_partial_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)buf, stride, bias,
-                          cos_t, sin_t, rot, tok_pos, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_pages,
-                          (__nv_bfloat16*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size);
+    typedef __nv_bfloat16 bf;
+#define LQ_GO(TI, TO) return launch_pdl(rope_partial_kernel<TI, TO>, dim3(T), dim3(256), 0, stream, (const TI*)buf, stride, \
+        (TO*)qout, qout_stride, bias, cos_t, sin_t, rot, tok_pos, tok_seq, slots, page_table, pt_stride, (TO*)k_pages, \
+        (TO*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size)
+    if (in_dtype == LQ_F32 && out_dtype == LQ_F32) LQ_GO(float, float);
+    if (in_dtype == LQ_BF16 && out_dtype == LQ_BF16) LQ_GO(bf, bf);
+    if (in_dtype == LQ_F32 && out_dtype == LQ_BF16) LQ_GO(float, bf);
+#undef LQ_GO
     return LQ_BAD_DTYPE;
 }
 
@@ -550,8 +554,8 @@ LQ_EXPORT int lq_activation(const void* x, void* out, int dtype, long long total
 }
 
 // x[r, c] *= sigmoid(gate[r, c]) (act 1) or silu(gate[r, c]) (act 2), in place; gate rows may be strided.
-template <typename T>
-__global__ void gate_mul_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int cols, size_t total, int act) {
+template <typename T, typename TG>
+__global__ void gate_mul_kernel(T* __restrict__ x, const TG* __restrict__ gate, int gate_stride, int cols, size_t total, int act) {
     pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -561,16 +565,19 @@ __global__ void gate_mul_kernel(T* __restrict__ x, const T* __restrict__ gate, i
     x[i] = from_f32<T>(to_f32(x[i]) * (act == 1 ? sg : g * sg));
 }
 
-LQ_EXPORT int lq_gate_mul(void* x, const void* gate, int gate_stride, int dtype, int rows, int cols, int act, cudaStream_t stream) {
+LQ_EXPORT int lq_gate_mul(void* x, const void* gate, int gate_stride, int dtype, int gate_dtype, int rows, int cols, int act,
+                          cudaStream_t stream) {
     const size_t total = (size_t)rows * cols;
     if (total == 0) return LQ_OK;
     if (act != 1 && act != 2) return LQ_BAD_SIZE;
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == LQ_F32)
-        return launch_pdl(gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride, cols, total, act);
-    if (dtype == LQ_BF16)
-        return launch_pdl(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x,
-                          (const __nv_bfloat16*)gate, gate_stride, cols, total, act);
+    typedef __nv_bfloat16 bf;
+    if (dtype == LQ_F32 && gate_dtype == LQ_F32)
+        return launch_pdl(gate_mul_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride, cols, total, act);
+    if (dtype == LQ_BF16 && gate_dtype == LQ_BF16)
+        return launch_pdl(gate_mul_kernel<bf, bf>, dim3(blocks), dim3(256), 0, stream, (bf*)x, (const bf*)gate, gate_stride, cols, total, act);
+    if (dtype == LQ_BF16 && gate_dtype == LQ_F32)
+        return launch_pdl(gate_mul_kernel<bf, float>, dim3(blocks), dim3(256), 0, stream, (bf*)x, (const float*)gate, gate_stride, cols, total, act);
     return LQ_BAD_DTYPE;
 }
 
@@ -595,14 +602,14 @@ LQ_EXPORT int lq_softcap(float* x, long long total, float cap, cudaStream_t stre
 // same order.
 constexpr int ATT_CHUNK = 128;
 
-template <typename T>
+template <typename T, typename TG>
 __global__ void __launch_bounds__(ATT_CHUNK)
 attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_pages,
                        const T* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ slots, T* __restrict__ out, int H, int Hkv, int hd,
                        int page_size, float scale, int window, int vd, const float* __restrict__ sink,
-                       const T* __restrict__ gate, int gate_stride) {
+                       const TG* __restrict__ gate, int gate_stride) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float sm[];
@@ -667,7 +674,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
     float o0 = acc0 / l, o1 = acc1 / l;
     if (gate) {
         // The output gate: each value times sigmoid of the gate's value at the same place.
-        const T* g = gate + (size_t)t * gate_stride + (size_t)h * vd;
+        const TG* g = gate + (size_t)t * gate_stride + (size_t)h * vd;
         if (tid < vd) o0 *= 1.f / (1.f + expf(-to_f32(g[tid])));
         if (tid + ATT_CHUNK < vd) o1 *= 1.f / (1.f + expf(-to_f32(g[tid + ATT_CHUNK])));
     }
@@ -680,18 +687,22 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                  const int* slots, void* out, int T, int H, int Hkv, int hd, int page_size,
                                  float scale, int window, int vd, const float* sink, const void* gate, int gate_stride,
-                                 cudaStream_t stream) {
+                                 int gate_dtype, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (vd <= 0) vd = hd;
     if (vd > 2 * ATT_CHUNK || H % Hkv) return LQ_BAD_SIZE;
     dim3 grid(T, H);
     size_t smem = (hd + 2 * ATT_CHUNK) * sizeof(float);
     if (dtype == LQ_F32)
-        return launch_pdl(attention_plain_kernel<float>, grid, dim3(ATT_CHUNK), smem, stream, (const float*)q, q_stride, (const float*)k_pages,
+        return launch_pdl(attention_plain_kernel<float, float>, grid, dim3(ATT_CHUNK), smem, stream, (const float*)q, q_stride, (const float*)k_pages,
             (const float*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, (float*)out, H, Hkv, hd, page_size, scale, window,
             vd, sink, (const float*)gate, gate_stride);
+    else if (dtype == LQ_BF16 && gate && gate_dtype == LQ_F32)
+        return launch_pdl(attention_plain_kernel<__nv_bfloat16, float>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
+            (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
+            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const float*)gate, gate_stride);
     else if (dtype == LQ_BF16)
-        return launch_pdl(attention_plain_kernel<__nv_bfloat16>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
+        return launch_pdl(attention_plain_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
             (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const __nv_bfloat16*)gate, gate_stride);
     else

@@ -245,16 +245,17 @@ def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_
         raise KernelError(f"attention: head sizes {hd}, {vd} exceed 256")
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != H):
         raise KernelError("attention: sink must be float32 [H]")
-    if gate is not None and (gate.dtype != q.dtype or gate.shape != (T, H * vd) or gate.stride(1) != 1):
-        raise KernelError("attention: the gate must be [T, H * vd] of the queries' dtype with unit column stride")
+    if gate is not None and (gate.dtype not in (q.dtype, torch.float32) or gate.shape != (T, H * vd) or gate.stride(1) != 1):
+        raise KernelError("attention: the gate must be [T, H * vd] of the queries' dtype or float32, with unit column stride")
     if out is None:
         out = torch.empty((T, H * vd), dtype=q.dtype, device=q.device)
     fn = _fn("plain_kernels", "lq_attention_plain", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                     c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+                                                     c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_p(q), q.stride(0), dtype_code(q), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0),
               _p(tok_pos), _p(tok_seq), _p(slots), _p(out), T, H, Hkv, hd, page_size, float(scale),
-              int(window or 0), vd, _p(sink), _p(gate), gate.stride(0) if gate is not None else 0, _stream()), "attention")
+              int(window or 0), vd, _p(sink), _p(gate), gate.stride(0) if gate is not None else 0,
+              dtype_code(gate) if gate is not None else F32, _stream()), "attention")
     return out
 
 
@@ -318,26 +319,33 @@ def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, eps: float, x: torch.Tensor
 
 def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: int, tok_pos, tok_seq, slots,
                  page_table, k_pages, v_pages, n_rot: int, k_first: int, Hkv: int, hd: int, vd: int, v_off: int,
-                 page_size: int) -> None:
-    """Biases, rotation of the first `rot` dimensions of each of the n_rot heads at the left of buf's rows (in
-    place), and, with a cache, the store of heads k_first.. into k_pages and of the values at column v_off into
-    v_pages.  bias: float32 over buf's columns, or None; cos/sin: float32 [positions, rot / 2]."""
+                 page_size: int, qout: torch.Tensor | None = None) -> None:
+    """Biases, then rotation of the first `rot` dimensions, for each of the n_rot heads at the left of buf's rows;
+    heads below k_first (queries) go to `qout` [T, k_first * hd] (default: back in place), heads k_first.. into
+    k_pages and the values at column v_off into v_pages where a cache is given.  bias: float32 over buf's
+    columns, or None; cos/sin: float32 [positions, rot / 2].  buf may be float32 while qout and the cache are
+    bfloat16 (a product's 32-bit sums, rounded once, after bias and rotation)."""
     T = buf.shape[0]
     if buf.stride(1) != 1:
         raise KernelError("rope_partial: rows must be contiguous")
+    if qout is None:
+        qout = buf
+    elif qout.shape[0] != T or qout.shape[1] < k_first * hd or qout.stride(1) != 1:
+        raise KernelError("rope_partial: qout must be [T, >= k_first * hd] with unit column stride")
     if rot:
         for t in (cos, sin):
             if t is None or t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != rot // 2 or not t.is_contiguous():
                 raise KernelError(f"rope_partial: cos/sin tables must be contiguous float32 [positions, {rot // 2}]")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() < (v_off + Hkv * vd if k_pages is not None else n_rot * hd)):
         raise KernelError("rope_partial: the bias must be float32 over the rows' columns")
-    if k_pages is not None and (k_pages.dtype != buf.dtype or v_pages.dtype != buf.dtype):
-        raise KernelError("rope_partial: the cache and the activations must have one dtype")
-    fn = _fn("plain_kernels", "lq_rope_partial", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(buf), dtype_code(buf), buf.stride(0), _p(bias), _p(cos), _p(sin), int(rot), _p(tok_pos), _p(tok_seq),
-              _p(slots), _p(page_table), page_table.stride(0) if page_table is not None else 0, _p(k_pages), _p(v_pages),
+    if k_pages is not None and (k_pages.dtype != qout.dtype or v_pages.dtype != qout.dtype):
+        raise KernelError("rope_partial: the cache and the queries must have one dtype")
+    fn = _fn("plain_kernels", "lq_rope_partial", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                  c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(buf), dtype_code(buf), buf.stride(0), _p(qout), dtype_code(qout), qout.stride(0), _p(bias), _p(cos), _p(sin),
+              int(rot), _p(tok_pos), _p(tok_seq), _p(slots), _p(page_table),
+              page_table.stride(0) if page_table is not None else 0, _p(k_pages), _p(v_pages),
               T, n_rot, k_first, Hkv, hd, vd, v_off, page_size, _stream()), "rope_partial")
 
 
@@ -367,10 +375,11 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
 def gate_mul(x: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch.Tensor:
     """x *= act(gate) in place; x [rows, cols] contiguous, gate a [rows, cols] view whose rows may be strided."""
     rows, cols = x.shape
-    if gate.dtype != x.dtype or tuple(gate.shape) != (rows, cols) or gate.stride(1) != 1:
-        raise KernelError("gate_mul: the gate must have x's shape and dtype and unit column stride")
-    fn = _fn("plain_kernels", "lq_gate_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(x, "x")), _p(gate), gate.stride(0), dtype_code(x), rows, cols, GATES[act], _stream()), "gate_mul")
+    if gate.dtype not in (x.dtype, torch.float32) or tuple(gate.shape) != (rows, cols) or gate.stride(1) != 1:
+        raise KernelError("gate_mul: the gate must have x's shape, x's dtype or float32, and unit column stride")
+    fn = _fn("plain_kernels", "lq_gate_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(gate), gate.stride(0), dtype_code(x), dtype_code(gate), rows, cols, GATES[act], _stream()),
+           "gate_mul")
     return x
 
 

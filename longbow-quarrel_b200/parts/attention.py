@@ -122,7 +122,12 @@ class Attention(Mixer):
         the rotated dimensions and the cache write in one kernel; attention with the sink in the
         denominator and the gate on the way out; the output projection."""
         H, G, hd, vd = self.H, self.Hkv, self.hd, self.vd
-        rows = linear.linear(h, self.w_qkv, self.runtime.act_dtype)
+        act = self.runtime.act_dtype
+        # With biases the product hands on its 32-bit sums: bias and rotation meet them before anything is
+        # rounded, as if the bias were added inside the product.
+        wide = self.bias and act != torch.float32
+        rows = linear.linear(h, self.w_qkv, torch.float32 if wide else act)
+        q = torch.empty((rows.shape[0], H * hd), dtype=act, device=rows.device) if wide else rows
         tables = self.position.tables() if self.position is not None else None
         if self.position is not None and tables is None:
             raise ValueError("attention: a position part without tables cannot be combined with the layer's options")
@@ -131,10 +136,10 @@ class Attention(Mixer):
         ops.rope_partial(rows, self.b_qkv, cos, sin, self.rot if tables is not None else 0, ctx.tok_pos, ctx.tok_seq,
                          ctx.slots, cache_view.page_table if store else None, cache_view.k_pages if store else None,
                          cache_view.v_pages if store else None, H + (G if self.own_kv else 0), H, G, hd, vd, v_off,
-                         cache_view.page_size)
+                         cache_view.page_size, qout=q if wide else None)
         g_off = H * hd + (G * (hd + vd) if self.own_kv else 0)
         gate = rows[:, g_off:g_off + H * vd] if self.gate is not None else None
-        out = attention_kernels.attention(rows, cache_view, ctx, H, G, hd, self.scale, self.window,
+        out = attention_kernels.attention(q, cache_view, ctx, H, G, hd, self.scale, self.window,
                                           next_w=self.w_o.tensor, vd=vd, sink=self.sinks, gate=gate)
         return self._project(out, residual, None)
 

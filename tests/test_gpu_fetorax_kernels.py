@@ -120,7 +120,8 @@ def test_biases_partial_rotation_and_cache_write(dtype, H, G, hd, vd, rot):
             u, w = v[:rot // 2].clone(), v[rot // 2:rot].clone()
             c, s = cos[pos[t]].double(), sin[pos[t]].double()
             v[:rot // 2], v[rot // 2:rot] = u * c - w * s, w * c + u * s
-            assert float((got[t, head * hd:(head + 1) * hd] - v).abs().max()) < tol * max(1.0, float(v.abs().max()))
+            if head < H:            # queries come back in place; keys go to the cache only
+                assert float((got[t, head * hd:(head + 1) * hd] - v).abs().max()) < tol * max(1.0, float(v.abs().max()))
             if head >= H:
                 stored = k_pages[pages[pos[t] // page], head - H, pos[t] % page].float().cpu().double()
                 assert float((stored - v).abs().max()) < tol * max(1.0, float(v.abs().max()))
@@ -130,6 +131,17 @@ def test_biases_partial_rotation_and_cache_write(dtype, H, G, hd, vd, rot):
             assert float((stored - v).abs().max()) < tol * max(1.0, float(v.abs().max()))
     # Columns beyond the values (a gate's, say) are left alone.
     assert torch.equal(dev[:, (H + G) * hd + G * vd:].cpu(), buf[:, (H + G) * hd + G * vd:])
+    if dtype == torch.bfloat16:
+        # Float32 rows in, bfloat16 queries and cache out: rounded once, after bias and rotation; the rows stay as they were.
+        wide = buf.float().to(DEV)
+        q16 = torch.zeros(T, H * hd, dtype=dtype, device=DEV)
+        k2, v2 = torch.zeros_like(k_pages), torch.zeros_like(v_pages)
+        ops.rope_partial(wide, bias.to(DEV), cos.to(DEV) if rot else None, sin.to(DEV) if rot else None, rot, _i32(pos),
+                         _i32([0] * T), _i32([0]), table, k2, v2, H + G, H, G, hd, vd, (H + G) * hd, page, qout=q16)
+        assert torch.equal(wide.cpu(), buf.float())
+        assert float((q16.float().cpu().double() - got[:, :H * hd]).abs().max()) < 2 * tol * float(got.abs().max())
+        assert float((k2.float() - k_pages.float()).abs().max()) < 2 * tol * float(got.abs().max())
+        assert float((v2.float() - v_pages.float()).abs().max()) < 2 * tol * float(got.abs().max())
 
 
 # ------------------------------------------------------------------ the recurrent scan
