@@ -440,7 +440,7 @@ def design_bench(args) -> int:
             "decode": {
                 "llama attention": times(per_launch(l["decode_kernels_us"], "attn_decode"), kv_read, 0.0),
                 "fetorax attention (with sink)": times(per_launch(f["decode_kernels_us"], "attn_decode"), kv_read, 0.0),
-                "fetorax recurrent scan": times(per_launch(f["decode_kernels_us"], "linear_scan"), state, 0.0),
+                "fetorax recurrent scan": times(per_launch(f["decode_kernels_us"], "linear_scan_single", "linear_scan"), state, 0.0),
             },
         }
         out[size] = {"fetorax": f, "llama": l, "times_the_roofline": roof,

@@ -10,8 +10,9 @@
 //
 // State, products and gates are float32 whatever the activations' storage is; q and k are rotated (optionally)
 // and scaled in float32 as they are staged, so nothing that enters the recurrence is rounded on the way.
-// One kernel serves prompts and single tokens: a sequence's tokens are walked in order from the state that the
-// step before left in the sequence's slot, so every way of cutting a prompt gives the same bits.
+// A sequence's tokens are walked in order from the state that the step before left in the sequence's slot, so a
+// prompt gives the same bits however it is cut into portions; steps of one token per sequence have a form of
+// their own (the same recurrence, sums in another order).
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -272,6 +273,84 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
     }
 }
 
+// The same recurrence for a step in which every sequence brings one token: nothing to pipeline, so the state
+// streams through once.  A block per (sequence, head, 32 value columns); a lane per column, so that a row of the
+// state is one contiguous read; the eight warps share the key rows (warp w: rows w, w + 8, ...) and their partial
+// outputs meet in shared memory, added in the order of the warps.
+constexpr int SS_WARPS = 8;
+
+template <typename T, bool MLSTM>
+__global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ float sm[];
+    const int dk = a.dk, dv = a.dv, dvx = dv + (MLSTM ? 1 : 0), dkx = dk + (MLSTM ? 1 : 0), H = a.H;
+    float* qs = sm;                              // [dk] rotated, scaled
+    float* ks = qs + dk;                         // [dk]
+    float* red = ks + dk;                        // [WARPS][32]
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int col = blockIdx.z * 32 + lane;
+    const bool live = col < dvx;
+    const int half = a.rot >> 1;
+    pdl_wait();
+    const int row = a.cu_rows[b];
+    const T* x = (const T*)a.qkv + (size_t)row * a.stride;
+    float* st = a.state + (long long)a.slots[b] * a.slot_stride + (size_t)h * dkx * dvx;
+    for (int j = tid; j < dk; j += SS_WARPS * 32) {
+        float qv = to_f32(x[a.q_off + h * dk + j]), kv = to_f32(x[a.k_off + h * dk + j]);
+        if (j < a.rot) {
+            const int f = j < half ? j : j - half, jp = j < half ? j + half : j - half;
+            const size_t at = (size_t)a.tok_pos[row] * half + f;
+            const float cs = a.cos_t[at], sn = j < half ? -a.sin_t[at] : a.sin_t[at];
+            qv = qv * cs + to_f32(x[a.q_off + h * dk + jp]) * sn;
+            kv = kv * cs + to_f32(x[a.k_off + h * dk + jp]) * sn;
+        }
+        qs[j] = qv * a.q_scale;
+        ks[j] = kv * a.k_scale;
+    }
+    float v = 0.f;
+    if (col < dv) v = to_f32(x[a.v_off + h * dv + col]);
+    else if (MLSTM && col == dv) v = 1.f;
+    float keep = MLSTM ? 0.f : a.decay[h], m_new = 0.f;
+    if (MLSTM) {
+        const float cap = a.gate_cap;
+        const float* g = a.gate_pre + (size_t)row * 2 * H;
+        const float li = cap * tanhf((g[h] + a.gate_bias[h]) / cap);
+        const float lf = log_sigmoid(cap * tanhf((g[H + h] + a.gate_bias[H + h]) / cap));
+        const float m_old = st[(size_t)dk * dvx + (live ? col : blockIdx.z * 32)];
+        m_new = fmaxf(lf + m_old, li);
+        keep = expf(lf + m_old - m_new);
+        v *= expf(li - m_new);
+        if (blockIdx.z == 0 && tid == 0) a.exp_neg_m[(size_t)row * H + h] = expf(-m_new);
+    }
+    __syncthreads();
+    float acc = 0.f;
+    if (live) {
+#pragma unroll 4
+        for (int r = warp; r < dk; r += SS_WARPS) {
+            float* sp = st + (size_t)r * dvx + col;
+            const float s_new = fmaf(keep, *sp, v * ks[r]);
+            *sp = s_new;
+            acc = fmaf(s_new, qs[r], acc);
+        }
+        if (MLSTM && warp == 0) st[(size_t)dk * dvx + col] = m_new;
+    }
+    red[warp * 32 + lane] = acc;
+    __syncthreads();
+    if (warp == 0 && live) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < SS_WARPS; ++w) total += red[w * 32 + lane];
+        a.out[((size_t)row * H + h) * dvx + col] = total;
+    }
+}
+
+template <typename T, bool MLSTM>
+static int scan_single_launch(const ScanArgs& a, int B, cudaStream_t stream) {
+    const int dvx = a.dv + (MLSTM ? 1 : 0);
+    const size_t smem = (size_t)(2 * a.dk + SS_WARPS * 32) * sizeof(float);
+    return launch_pdl(linear_scan_single_kernel<T, MLSTM>, dim3(B, a.H, (dvx + 31) / 32), dim3(SS_WARPS * 32), smem, stream, a);
+}
+
 template <typename T, bool MLSTM>
 static int scan_launch(const ScanArgs& a, int B, cudaStream_t stream) {
     const int dvx = a.dv + (MLSTM ? 1 : 0);
@@ -295,12 +374,22 @@ LQ_EXPORT int lq_linear_scan(const void* qkv, int dtype, int stride, int q_off, 
                              const float* sin_t, int rot, const int* tok_pos, const float* gate_pre,
                              const float* gate_bias, float gate_cap, const float* decay, float q_scale, float k_scale,
                              float* state, long long slot_stride, const int* cu_rows, const int* slots, float* out,
-                             float* exp_neg_m, int B, int H, int dk, int dv, int mlstm, cudaStream_t stream) {
+                             float* exp_neg_m, int B, int H, int dk, int dv, int mlstm, int single, cudaStream_t stream) {
     if (B <= 0) return LQ_OK;
     if (rot % 2 || rot > dk || (rot && (!cos_t || !sin_t))) return LQ_BAD_SIZE;
     if (mlstm ? (!gate_pre || !gate_bias || !exp_neg_m) : !decay) return LQ_BAD_SIZE;
     ScanArgs a{qkv, stride, q_off, k_off, v_off, cos_t, sin_t, rot, tok_pos, gate_pre, gate_bias, gate_cap, decay,
                q_scale, k_scale, state, slot_stride, cu_rows, slots, out, exp_neg_m, H, dk, dv};
+    if (single) {
+        // Every sequence brings exactly one token (row cu_rows[b]).
+        if (dk > 256) return LQ_BAD_SIZE;
+        if (dtype == LQ_F32)
+            return mlstm ? scan_single_launch<float, true>(a, B, stream) : scan_single_launch<float, false>(a, B, stream);
+        if (dtype == LQ_BF16)
+            return mlstm ? scan_single_launch<__nv_bfloat16, true>(a, B, stream)
+                         : scan_single_launch<__nv_bfloat16, false>(a, B, stream);
+        return LQ_BAD_DTYPE;
+    }
     if (dtype == LQ_F32) return mlstm ? scan_launch<float, true>(a, B, stream) : scan_launch<float, false>(a, B, stream);
     if (dtype == LQ_BF16)
         return mlstm ? scan_launch<__nv_bfloat16, true>(a, B, stream) : scan_launch<__nv_bfloat16, false>(a, B, stream);

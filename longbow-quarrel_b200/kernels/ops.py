@@ -386,14 +386,16 @@ def gate_mul(x: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch
 # ------------------------------------------------------------------ mixers with a matrix state per head
 def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, cu_rows, slots, tok_pos,
                 B: int, H: int, dk: int, dv: int, q_scale: float = 1.0, k_scale: float = 1.0,
-                decay: torch.Tensor | None = None, gates: tuple | None = None, rot: tuple | None = None):
+                decay: torch.Tensor | None = None, gates: tuple | None = None, rot: tuple | None = None,
+                single: bool = False):
     """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t for the rows of B sequences (rows cu_rows[b] ..
     cu_rows[b+1] of qkv belong to the sequence in slot slots[b]), from and into `state` (float32
     [slots, H, dk (+1), dv (+1)]).  decay: float32 [H] (a_t fixed, b_t = 1).  gates = (pre [rows, 2H] float32,
     bias [2H] float32, cap): exponential input gate and sigmoid forget gate with a running maximum; the state then
     has one more row (the maximum) and one more column (the normaliser).  rot = (cos, sin, dims): q and k are
-    rotated as they are read.  Returns the raw outputs float32 [rows, H, dv (+1)] and, with gates,
-    exp(-maximum) float32 [rows, H]."""
+    rotated as they are read.  single: every sequence brings exactly one token (the kernel then streams the
+    state once, without staging chunks of tokens).  Returns the raw outputs float32 [rows, H, dv (+1)] and,
+    with gates, exp(-maximum) float32 [rows, H]."""
     rows = qkv.shape[0]
     mlstm = gates is not None
     dvx, dkx = dv + int(mlstm), dk + int(mlstm)
@@ -417,10 +419,11 @@ def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
     fn = _fn("recurrent", "lq_linear_scan", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_float, c_void_p,
                                              c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                             c_int, c_void_p])
+                                             c_int, c_int, c_void_p])
     _check(fn(_p(qkv), dtype_code(qkv), qkv.stride(0), q_off, k_off, v_off, _p(cos), _p(sin), int(dims), _p(tok_pos),
               _p(pre), _p(bias), float(cap), _p(decay), float(q_scale), float(k_scale), _p(state), state.stride(0),
-              _p(cu_rows), _p(slots), _p(out), _p(enm), B, H, dk, dv, int(mlstm), _stream()), "linear_scan")
+              _p(cu_rows), _p(slots), _p(out), _p(enm), B, H, dk, dv, int(mlstm), int(single and rows == B), _stream()),
+           "linear_scan", 1, "linear_scan:single" if single and rows == B else None)
     return out, enm
 
 

@@ -18,9 +18,10 @@ fixed-size state of the sequence's slot, which is zero when a sequence starts:
              then W_o.
 
 Gates, decays, the state and the per-head norms are 32-bit in both precisions; the
-gates' pre-activations come from a 32-bit product of their own.  One kernel walks a
-sequence's tokens in order for prompts and for single tokens alike
-(`csrc/recurrent.cu`), so every way of cutting a prompt gives the same result.
+gates' pre-activations come from a 32-bit product of their own.  A sequence's tokens
+are walked in order from the state in its slot (`csrc/recurrent.cu`: one kernel for
+prompts and portions, one for steps of a single token per sequence), so a position's
+result does not depend on how its prompt was cut, beyond rounding.
 """
 from __future__ import annotations
 
@@ -96,7 +97,7 @@ class Retention(_MatrixStateMixer):
             cos, sin = self.position.tables()
             rot = (cos, sin, self.position.rotary_dims)
         raw, _ = ops.linear_scan(rows, 0, H * dk, 2 * H * dk, cache_view, ctx.cu_rows, ctx.slots, ctx.tok_pos, ctx.B,
-                                 H, dk, dv, k_scale=dk ** -0.5, decay=self.decay, rot=rot)
+                                 H, dk, dv, k_scale=dk ** -0.5, decay=self.decay, rot=rot, single=ctx.decode)
         g_off = 2 * H * dk + H * dv
         out = ops.head_norm_gate(raw, dv, self.eps, self.runtime.act_dtype, gate=rows[:, g_off:g_off + H * dv], act="silu")
         return self._finish(out, residual)
@@ -135,7 +136,7 @@ class MLSTM(_MatrixStateMixer):
         rows = linear.linear(h, self.w_in, self.runtime.act_dtype)
         pre = ops.small_proj(h, self.w_gates)         # the gates enter the recurrence: a 32-bit product of their own
         raw, enm = ops.linear_scan(rows, 0, H * dk, 2 * H * dk, cache_view, ctx.cu_rows, ctx.slots, ctx.tok_pos, ctx.B,
-                                   H, dk, dv, q_scale=dk ** -0.5, gates=(pre, self.b_gates, self.cap))
+                                   H, dk, dv, q_scale=dk ** -0.5, gates=(pre, self.b_gates, self.cap), single=ctx.decode)
         g_off = 2 * H * dk + H * dv
         out = ops.head_norm_gate(raw, dv, self.eps, self.runtime.act_dtype, exp_neg_m=enm, weight=self.head_weight,
                                  gate=rows[:, g_off:g_off + H * dv], act="sigmoid")

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_fetorax
-from fetorax_models import CONFIGS, F32_TOL, bound, load, make_folder, row_errors, tokens
+from fetorax_models import CONFIGS, bound, load, make_folder, row_errors, tokens
 from trace_tools import ROOT, Trace, run_trace, split, trace_batches, trace_chunked, trace_last_one_by_one, trace_mixed, trace_whole
 
 pytestmark = pytest.mark.gpu
@@ -67,8 +67,8 @@ def test_one_layer_of_each_mixer_whole_and_token_by_token(tmp_path, name, dtype)
     single = np.stack([eng.step([(s, [t])], [[0]]).cpu().numpy()[0] for t in toks])
     eng.end_sequence(s)
     assert row_errors(single, ref).max() < tol
-    # Prompt and single tokens go through the same recurrence and the same order of sums.
-    assert row_errors(single, whole).max() < (F32_TOL if dtype == "float32" else tol)
+    # Prompt and single tokens go through the same recurrence.
+    assert row_errors(single, whole).max() < tol
     eng.close()
 
 
@@ -98,12 +98,18 @@ def test_every_cut_of_every_request_matches_plain(tmp_path, name, dtype):
     for what, rows in cuts.items():
         assert len(rows) == (33 * len(requests) if what == "tail" else sum(LENGTHS.values())), what
         _check(rows, requests, folder, dtype, what)
-    # The cuts against one another: in float32 to 2e-5, in bfloat16 within the same noise.
-    for what in ("tail", "batched", "portions", "mixed"):
-        for (rid, pos), row in cuts[what].items():
-            if dtype == "float32":
-                err = float(row_errors(row, cuts["whole"][(rid, pos)]))
-                assert err < F32_TOL, f"{what} against whole: {rid} position {pos}: {err:.3g}"
+    # The cuts against one another, in float32: prompts and single tokens of the recurrent layers run through two
+    # kernels that add in another order, so two cuts, each within the request's own float32 bound of the exact
+    # result (2e-5 for most requests), lie within twice that of each other.
+    if dtype == "float32":
+        for rid, toks in requests.items():
+            cfg, weights, ref = _plain(folder, toks)
+            tol = bound(dtype, cfg, weights, toks, ref)
+            for what in ("tail", "batched", "portions", "mixed"):
+                for (r, pos), row in cuts[what].items():
+                    if r == rid:
+                        err = float(row_errors(row, cuts["whole"][(r, pos)]))
+                        assert err < 2 * tol, f"{what} against whole: {rid} position {pos}: {err:.3g}, bound {2 * tol:.3g}"
 
 
 # ------------------------------------------------------------------ slots and pages used again, long decoding

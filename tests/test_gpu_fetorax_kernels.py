@@ -325,3 +325,42 @@ def test_a_projection_onto_few_outputs_in_32_bit(rows, N, K):
     # a row's result does not depend on the rows beside it
     alone = ops.small_proj(x[:1].contiguous().to(DEV), w.to(DEV))
     assert torch.equal(alone[0], ops.small_proj(x.to(DEV), w.to(DEV))[0])
+
+
+@pytest.mark.parametrize("mlstm", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dk,dv,rot", [(2, 16, 24, 8), (1, 72, 5, 0), (3, 136, 33, 136), (2, 64, 64, 32), (1, 256, 70, 2)])
+def test_the_single_token_form_of_the_scan_agrees_with_the_chunked_one(H, dk, dv, rot, mlstm, dtype):
+    """Five sequences in shuffled slots with states left by prompts of unequal lengths; then one token each through
+    the kernel for prompts and through the one for single tokens: the same outputs and the same states."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(dk + dv + int(mlstm))
+    B, lens, slots = 5, [40, 1, 17, 64, 3], [6, 0, 3, 1, 4]
+    width = H * (2 * dk + dv) + 5
+    cos = torch.rand(80, max(rot // 2, 1), generator=gen).to(DEV).contiguous()
+    sin = torch.rand(80, max(rot // 2, 1), generator=gen).to(DEV).contiguous()
+    decay = torch.linspace(0.9, 0.999, H).to(DEV)
+    bias = torch.randn(2 * H, generator=gen).to(DEV)
+
+    def call(rows, state, cu, pos, n_seq, single):
+        kw = dict(gates=(torch.randn(rows.shape[0], 2 * H, generator=torch.Generator().manual_seed(rows.shape[0])).mul(4.0).to(DEV),
+                         bias, 6.0), q_scale=dk ** -0.5) if mlstm else \
+            dict(decay=decay, k_scale=dk ** -0.5, rot=(cos[:, :rot // 2].contiguous(), sin[:, :rot // 2].contiguous(), rot) if rot else None)
+        return ops.linear_scan(rows.to(DEV), 3, 3 + H * dk, 3 + 2 * H * dk, state, _i32(cu), _i32(slots[:n_seq]), _i32(pos), n_seq,
+                               H, dk, dv, single=single, **kw)
+
+    state = torch.zeros(8, H, dk + int(mlstm), dv + int(mlstm), device=DEV)
+    prompt = torch.randn(sum(lens), width, generator=gen).to(dtype)
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    call(prompt, state, cu, np.concatenate([np.arange(n) for n in lens]), B, False)
+    step = torch.randn(B, width, generator=gen).to(dtype)
+    s_chunked, s_single = state.clone(), state.clone()
+    raw_c, enm_c = call(step, s_chunked, np.arange(B + 1), lens, B, False)
+    raw_s, enm_s = call(step, s_single, np.arange(B + 1), lens, B, True)
+    scale = float(raw_c.abs().max())
+    assert float((raw_s - raw_c).abs().max()) < 1e-5 * scale
+    assert float((s_single - s_chunked).abs().max()) < 1e-5 * float(s_chunked.abs().max())
+    if mlstm:
+        assert float((enm_s - enm_c).abs().max()) < 1e-5 * float(enm_c.abs().max())
+    untouched = [i for i in range(8) if i not in slots]
+    assert float(s_single[untouched].abs().max()) == 0.0
