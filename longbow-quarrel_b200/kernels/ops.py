@@ -433,6 +433,8 @@ def small_proj(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     rows, K = x.shape
     if w.shape[1] != K:
         raise KernelError(f"small_proj: input width {K} does not match weight width {w.shape[1]}")
+    if 16 * K > 200 * 1024:
+        return gemm_plain(x, w, torch.float32)          # rows too wide for the kernel's shared memory: the tiled product
     out = torch.empty((rows, w.shape[0]), dtype=torch.float32, device=x.device)
     fn = _fn("recurrent", "lq_small_proj", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(_p(_contig(x, "x")), dtype_code(x), _p(_contig(w, "w")), dtype_code(w), _p(out), rows, w.shape[0], K, _stream()),

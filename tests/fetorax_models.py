@@ -114,7 +114,7 @@ def row_errors(got: np.ndarray, ref: np.ndarray) -> np.ndarray:
     return np.sqrt(((got - ref) ** 2).mean(-1)) / np.maximum(np.sqrt((ref ** 2).mean(-1)), 1e-30)
 
 
-F32_TOL = 2e-5        # two float32 runs of the same kernels on another cut of a request, per row
+F32_TOL = 2e-5        # the floor of every float32 bound, per row
 
 
 def bound(dtype: str, cfg: dict, weights: dict, toks, exact: np.ndarray) -> float:
