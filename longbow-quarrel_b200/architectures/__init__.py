@@ -1,1 +1,1 @@
-from . import fetorax, llama  # noqa: F401  (registers LlamaForCausalLM and Fetorax)
+from . import fetorax, llama, zoporax  # noqa: F401  (registers LlamaForCausalLM, Fetorax and Zoporax)

@@ -22,7 +22,7 @@ NO_PAGE = -1
 class PagedKVGroup(CacheGroup):
     def __init__(self, entries: list[int], n_kv_heads: int, head_dim: int, window: int | None, n_pages: int,
                  page_size: int, max_slots: int, max_pages_per_seq: int, dtype: torch.dtype, device,
-                 v_head_dim: int | None = None):
+                 v_head_dim: int | None = None, values: bool = True):
         self.entries = list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.n_kv_heads, self.head_dim, self.window = n_kv_heads, head_dim, window
@@ -33,7 +33,8 @@ class PagedKVGroup(CacheGroup):
         # which needs finite values there: the pool starts zero-filled, and a page that is handed out
         # again has the rows that its new owner's step does not write cleared first (`_to_clear`).
         self.k_pages = torch.zeros(shape, dtype=dtype, device=device)
-        self.v_pages = torch.zeros((*shape[:4], self.v_head_dim), dtype=dtype, device=device)
+        # values=False: the mixer reads its values out of the keys' rows, and there is no second pool.
+        self.v_pages = torch.zeros((*shape[:4], self.v_head_dim), dtype=dtype, device=device) if values else None
         self.table = np.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=np.int32)
         self.table_dev = torch.full((max_slots, max_pages_per_seq), NO_PAGE, dtype=torch.int32, device=device)
         self._free = list(range(n_pages - 1, -1, -1))
@@ -144,17 +145,18 @@ class PagedKVGroup(CacheGroup):
             todo, self._to_clear = self._to_clear, []
             if self.k_pages.is_cuda:
                 from ..kernels import ops
-                ops.clear_page_tails(self.k_pages, self.v_pages, todo)
+                ops.clear_page_tails(self.k_pages, self.v_pages if self.v_pages is not None else self.k_pages, todo)
             else:                                   # bookkeeping tests keep their pools on the CPU
                 for page, first in todo:
                     self.k_pages[:, page, :, first:].zero_()
-                    self.v_pages[:, page, :, first:].zero_()
+                    if self.v_pages is not None:
+                        self.v_pages[:, page, :, first:].zero_()
 
     def view(self, entry: int) -> "KVView":
         return KVView(self, entry)
 
     def nbytes(self) -> int:
-        return (self.k_pages.numel() + self.v_pages.numel()) * self.k_pages.element_size()
+        return (self.k_pages.numel() + (self.v_pages.numel() if self.v_pages is not None else 0)) * self.k_pages.element_size()
 
     def pages_in_use(self) -> int:
         return self.n_pages - len(self._free)
@@ -166,7 +168,7 @@ class KVView:
     def __init__(self, group: PagedKVGroup, entry: int):
         i = group.index[entry]
         self.k_pages = group.k_pages[i]
-        self.v_pages = group.v_pages[i]
+        self.v_pages = group.v_pages[i] if group.v_pages is not None else None
         self.page_table = group.table_dev
         self.page_size = group.page_size
         self.window = group.window

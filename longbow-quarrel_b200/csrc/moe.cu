@@ -1,0 +1,189 @@
+// A feed-forward that sends each token to a few of many small experts.
+//
+//   lq_moe_route   router logits -> the chosen experts of every token and their weights
+//   lq_moe_up      u[t, j, :] = act(W_up[e(t, j)] h[t])             for the j-th chosen expert of token t
+//   lq_moe_down    y[t, :] = sum_j w(t, j) W_down[e(t, j)] u[t, j, :], in the order of j; optionally
+//                  + sigmoid(z_s[t]) * shared[t, :], and the whole added into the float32 stream
+//
+// Routing: scores s = sigmoid(z).  The experts form `groups` equal groups of neighbours; a group's score is the
+// sum of its two largest scores; only experts of the `keep` best groups can be chosen; of those the `top` with
+// the largest scores are (ties go to the lower index).  Weights: the chosen scores over their sum (+ 1e-20),
+// times `route_scale`.  Everything here is float32.
+//
+// Every token streams the matrices of its own experts (a warp per output row, lanes along the contraction), so a
+// step of few tokens reads each chosen expert about once; tokens that share an expert meet in L2.
+#include "common.cuh"
+#include <math_constants.h>
+
+constexpr int MR_WARPS = 4;
+
+// Index of the largest value among vals[0..n) (ties: the lowest index), found by a whole warp.
+__device__ __forceinline__ int warp_argmax(const float* vals, int n, int lane) {
+    float best = -CUDART_INF_F;
+    int at = 0x7fffffff;
+    for (int i = lane; i < n; i += 32)
+        if (vals[i] > best) { best = vals[i]; at = i; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    return at;
+}
+
+__global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const float* __restrict__ z, int z_stride, int* __restrict__ ids,
+                                                                  float* __restrict__ weights, int T, int E, int groups, int keep,
+                                                                  int top, float route_scale) {
+    pdl_launch_dependents();
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * MR_WARPS + warp;
+    float* score = sm + (size_t)warp * (2 * E + groups);      // [E] the scores
+    float* cand = score + E;                                  // [E] the scores still to be chosen from (-1: not)
+    float* gs = cand + E;                                     // [groups]
+    pdl_wait();
+    if (t >= T) return;
+    const int per = E / groups;
+    for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-z[(size_t)t * z_stride + e]));
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+        float a = -1.f, b = -1.f;                             // the two largest of the group
+        for (int i = 0; i < per; ++i) {
+            const float v = score[g * per + i];
+            if (v > a) { b = a; a = v; } else if (v > b) b = v;
+        }
+        gs[g] = a + (per > 1 ? b : 0.f);
+    }
+    for (int e = lane; e < E; e += 32) cand[e] = -1.f;
+    __syncwarp();
+    for (int n = 0; n < keep; ++n) {
+        const int g = warp_argmax(gs, groups, lane);
+        __syncwarp();
+        for (int i = lane; i < per; i += 32) cand[g * per + i] = score[g * per + i];
+        if (lane == 0) gs[g] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    float sum = 0.f;
+    for (int n = 0; n < top; ++n) {
+        const int e = warp_argmax(cand, E, lane);
+        __syncwarp();
+        sum += score[e];
+        if (lane == 0) { ids[(size_t)t * top + n] = e; cand[e] = -2.f; }
+        __syncwarp();
+    }
+    const float inv = route_scale / (sum + 1e-20f);
+    for (int n = lane; n < top; n += 32) weights[(size_t)t * top + n] = score[ids[(size_t)t * top + n]] * inv;
+}
+
+LQ_EXPORT int lq_moe_route(const float* z, int z_stride, int* ids, float* weights, int T, int E, int groups, int keep, int top,
+                           float route_scale, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (E < 1 || groups < 1 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)) return LQ_BAD_SIZE;
+    const size_t smem = (size_t)MR_WARPS * (2 * E + groups) * sizeof(float);
+    if (smem > 200 * 1024) return LQ_BAD_SIZE;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(moe_route_kernel, dim3((T + MR_WARPS - 1) / MR_WARPS), dim3(MR_WARPS * 32), smem, stream, z, z_stride, ids,
+                      weights, T, E, groups, keep, top, route_scale);
+}
+
+// act: 0 none, 1 gelu (erf), 2 gelu (tanh form), 3 silu, 4 relu
+__device__ __forceinline__ float moe_act(float v, int act) {
+    switch (act) {
+        case 1: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+        case 2: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        case 3: return v / (1.f + expf(-v));
+        case 4: return fmaxf(v, 0.f);
+        default: return v;
+    }
+}
+
+constexpr int MX_WARPS = 8;
+constexpr int MX_PER_WARP = 4;        // output rows a warp makes one after the other
+
+// grid (T * top, ceil(F / (MX_WARPS * MX_PER_WARP))): h[t] in shared memory as float32; a warp per output row.
+template <typename T>
+__global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up,
+                                                               const int* __restrict__ ids, T* __restrict__ u, int top, int D,
+                                                               int F, int act) {
+    pdl_launch_dependents();
+    extern __shared__ float xs[];                 // [D]
+    const int pair = blockIdx.x, t = pair / top, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();
+    for (int d = tid; d < D; d += MX_WARPS * 32) xs[d] = to_f32(h[(size_t)t * D + d]);
+    const int e = ids[pair];
+    __syncthreads();
+    const T* w = w_up + (size_t)e * F * D;
+    for (int i = 0; i < MX_PER_WARP; ++i) {
+        const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
+        if (f >= F) break;
+        const T* wr = w + (size_t)f * D;
+        float s = 0.f;
+        for (int d = lane; d < D; d += 32) s = fmaf(xs[d], to_f32(wr[d]), s);
+        s = warp_sum(s);
+        if (lane == 0) u[(size_t)pair * F + f] = from_f32<T>(moe_act(s, act));
+    }
+}
+
+// grid (T, ceil(D / (MX_WARPS * MX_PER_WARP))): the token's `top` rows of u in shared memory; a warp per output.
+template <typename T>
+__global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __restrict__ u, const T* __restrict__ w_down,
+                                                                 const int* __restrict__ ids, const float* __restrict__ weights,
+                                                                 const float* __restrict__ shared, const float* __restrict__ zs,
+                                                                 int zs_stride, float* __restrict__ x, int accumulate, int top,
+                                                                 int D, int F) {
+    pdl_launch_dependents();
+    extern __shared__ float us[];                 // [top][F]
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();
+    for (int i = tid; i < top * F; i += MX_WARPS * 32) us[i] = to_f32(u[(size_t)t * top * F + i]);
+    __syncthreads();
+    const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
+    for (int i = 0; i < MX_PER_WARP; ++i) {
+        const int d = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
+        if (d >= D) break;
+        float y = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const T* wr = w_down + ((size_t)ids[(size_t)t * top + j] * D + d) * F;
+            float s = 0.f;
+            for (int f = lane; f < F; f += 32) s = fmaf(us[j * F + f], to_f32(wr[f]), s);
+            y = fmaf(weights[(size_t)t * top + j], warp_sum(s), y);
+        }
+        if (lane == 0) {
+            if (shared) y = fmaf(sg, shared[(size_t)t * D + d], y);
+            float* o = x + (size_t)t * D + d;
+            *o = accumulate ? *o + y : y;
+        }
+    }
+}
+
+LQ_EXPORT int lq_moe_up(const void* h, const void* w_up, const int* ids, void* u, int dtype, int T, int top, int D, int F, int act,
+                        cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (act < 0 || act > 4 || (size_t)D * 4 > 200 * 1024) return LQ_BAD_SIZE;
+    dim3 grid(T * top, (F + MX_WARPS * MX_PER_WARP - 1) / (MX_WARPS * MX_PER_WARP));
+    const size_t smem = (size_t)D * sizeof(float);
+    typedef __nv_bfloat16 bf;
+#define LQ_GO(TT) do { if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return launch_pdl(moe_up_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)h, (const TT*)w_up, ids, (TT*)u, top, D, F, act); } while (0)
+    if (dtype == LQ_F32) LQ_GO(float);
+    if (dtype == LQ_BF16) LQ_GO(bf);
+#undef LQ_GO
+    return LQ_BAD_DTYPE;
+}
+
+LQ_EXPORT int lq_moe_down(const void* u, const void* w_down, const int* ids, const float* weights, const float* shared,
+                          const float* zs, int zs_stride, float* x, int accumulate, int dtype, int T, int top, int D, int F,
+                          cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    const size_t smem = (size_t)top * F * sizeof(float);
+    if (smem > 200 * 1024) return LQ_BAD_SIZE;
+    dim3 grid(T, (D + MX_WARPS * MX_PER_WARP - 1) / (MX_WARPS * MX_PER_WARP));
+    typedef __nv_bfloat16 bf;
+#define LQ_GO(TT) do { if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return launch_pdl(moe_down_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)u, (const TT*)w_down, ids, weights, \
+                          shared, zs, zs_stride, x, accumulate, top, D, F); } while (0)
+    if (dtype == LQ_F32) LQ_GO(float);
+    if (dtype == LQ_BF16) LQ_GO(bf);
+#undef LQ_GO
+    return LQ_BAD_DTYPE;
+}

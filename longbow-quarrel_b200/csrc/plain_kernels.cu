@@ -500,12 +500,13 @@ LQ_EXPORT int lq_rope_partial(const void* buf, int in_dtype, int stride, void* q
 }
 
 // ------------------------------------------------------------------ activations, soft cap
-// out = act(x), element by element, in float32: 0 relu(x)^2, 1 gelu (tanh form), 2 silu, 3 relu.
+// out = act(x), element by element, in float32: 0 relu(x)^2, 1 gelu (tanh form), 2 silu, 3 relu, 4 gelu (erf form).
 __device__ __forceinline__ float activation(float v, int act) {
     switch (act) {
         case 0: { float r = fmaxf(v, 0.f); return r * r; }
         case 1: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
         case 2: return v / (1.f + expf(-v));
+        case 4: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
         default: return fmaxf(v, 0.f);
     }
 }
@@ -535,7 +536,7 @@ __global__ void activation_vec_kernel(const uint4* __restrict__ x, uint4* __rest
 
 LQ_EXPORT int lq_activation(const void* x, void* out, int dtype, long long total, int act, cudaStream_t stream) {
     if (total <= 0) return LQ_OK;
-    if (act < 0 || act > 3) return LQ_BAD_SIZE;
+    if (act < 0 || act > 4) return LQ_BAD_SIZE;
     const int vec = dtype == LQ_F32 ? 4 : 8;
     if ((dtype == LQ_F32 || dtype == LQ_BF16) && total % vec == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
         const size_t pieces = (size_t)total / vec;
@@ -551,6 +552,52 @@ LQ_EXPORT int lq_activation(const void* x, void* out, int dtype, long long total
         return launch_pdl(activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x,
                           (__nv_bfloat16*)out, (size_t)total, act);
     return LQ_BAD_DTYPE;
+}
+
+// out[t, f] = act(gu[t, f] + b[f]) * (gu[t, F + f] + b[F + f]): a gated feed-forward's two halves (gate columns, then up
+// columns) with their biases (float32 [2F], or none), the activation in float32.
+template <typename TI, typename TO>
+__global__ void gated_act_kernel(const TI* __restrict__ gu, const float* __restrict__ bias, TO* __restrict__ out, size_t total,
+                                 int F, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / F;
+    const int f = i % F;
+    float g = to_f32(gu[t * 2 * F + f]), u = to_f32(gu[t * 2 * F + F + f]);
+    if (bias) { g += bias[f]; u += bias[F + f]; }
+    out[i] = from_f32<TO>(activation(g, act) * u);
+}
+
+LQ_EXPORT int lq_gated_act(const void* gu, int in_dtype, const float* bias, void* out, int out_dtype, int T, int F, int act,
+                           cudaStream_t stream) {
+    const size_t total = (size_t)T * F;
+    if (total == 0) return LQ_OK;
+    if (act < 0 || act > 4) return LQ_BAD_SIZE;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    typedef __nv_bfloat16 bf;
+    if (in_dtype == LQ_F32 && out_dtype == LQ_F32)
+        return launch_pdl(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, bias, (float*)out, total, F, act);
+    if (in_dtype == LQ_F32 && out_dtype == LQ_BF16)
+        return launch_pdl(gated_act_kernel<float, bf>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, bias, (bf*)out, total, F, act);
+    if (in_dtype == LQ_BF16 && out_dtype == LQ_BF16)
+        return launch_pdl(gated_act_kernel<bf, bf>, dim3(blocks), dim3(256), 0, stream, (const bf*)gu, bias, (bf*)out, total, F, act);
+    return LQ_BAD_DTYPE;
+}
+
+// x[t, d] += bias[d] (float32 rows of the stream; a projection's bias that its residual epilogue does not add).
+__global__ void add_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, size_t total, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] += bias[i % D];
+}
+
+LQ_EXPORT int lq_add_bias(float* x, const float* bias, int T, int D, cudaStream_t stream) {
+    const size_t total = (size_t)T * D;
+    if (total == 0) return LQ_OK;
+    return launch_pdl(add_bias_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, bias, total, D);
 }
 
 // x[r, c] *= sigmoid(gate[r, c]) (act 1) or silu(gate[r, c]) (act 2), in place; gate rows may be strided.

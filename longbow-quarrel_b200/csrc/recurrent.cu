@@ -42,7 +42,10 @@ struct ScanArgs {
     float* out;                  // [rows, H, dvx] raw S^T q (mlstm: column dv holds n . q)
     float* exp_neg_m;            // mlstm: [rows, H] exp(-m_t)
     int H, dk, dv;
+    int in_act;                  // 0: q, k and v enter as stored; 1: each goes through silu first (in float32)
 };
+
+__device__ __forceinline__ float scan_in(float x, int act) { return act ? x / (1.f + expf(-x)) : x; }
 
 // One block walks the tokens of one (sequence, head, 16 value columns) in chunks of SC_CHUNK; a warp owns a column,
 // lane r the key rows r, r + 32, ... of it (KR of them).  While a chunk is multiplied, the next chunk's q, k and v
@@ -100,8 +103,8 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
         for (int i = 0; i < KR; ++i) {
             q_pf[i] = k_pf[i] = 0.f;
             if (e_tok[i] < n) {
-                q_pf[i] = to_f32(rows[e_off[i] + a.q_off]);
-                k_pf[i] = to_f32(rows[e_off[i] + a.k_off]);
+                q_pf[i] = scan_in(to_f32(rows[e_off[i] + a.q_off]), a.in_act);
+                k_pf[i] = scan_in(to_f32(rows[e_off[i] + a.k_off]), a.in_act);
             }
         }
         if (half) {
@@ -119,7 +122,7 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
         if (v_tok < SC_CHUNK) {
             v_pf = 0.f;
             if (v_tok < n) {
-                if (v_col < dv) v_pf = to_f32(rows[v_at]);
+                if (v_col < dv) v_pf = scan_in(to_f32(rows[v_at]), a.in_act);
                 else if (MLSTM && v_col == dv) v_pf = 1.f;
             }
         }
@@ -296,19 +299,19 @@ __global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanA
     const T* x = (const T*)a.qkv + (size_t)row * a.stride;
     float* st = a.state + (long long)a.slots[b] * a.slot_stride + (size_t)h * dkx * dvx;
     for (int j = tid; j < dk; j += SS_WARPS * 32) {
-        float qv = to_f32(x[a.q_off + h * dk + j]), kv = to_f32(x[a.k_off + h * dk + j]);
+        float qv = scan_in(to_f32(x[a.q_off + h * dk + j]), a.in_act), kv = scan_in(to_f32(x[a.k_off + h * dk + j]), a.in_act);
         if (j < a.rot) {
             const int f = j < half ? j : j - half, jp = j < half ? j + half : j - half;
             const size_t at = (size_t)a.tok_pos[row] * half + f;
             const float cs = a.cos_t[at], sn = j < half ? -a.sin_t[at] : a.sin_t[at];
-            qv = qv * cs + to_f32(x[a.q_off + h * dk + jp]) * sn;
-            kv = kv * cs + to_f32(x[a.k_off + h * dk + jp]) * sn;
+            qv = qv * cs + scan_in(to_f32(x[a.q_off + h * dk + jp]), a.in_act) * sn;
+            kv = kv * cs + scan_in(to_f32(x[a.k_off + h * dk + jp]), a.in_act) * sn;
         }
         qs[j] = qv * a.q_scale;
         ks[j] = kv * a.k_scale;
     }
     float v = 0.f;
-    if (col < dv) v = to_f32(x[a.v_off + h * dv + col]);
+    if (col < dv) v = scan_in(to_f32(x[a.v_off + h * dv + col]), a.in_act);
     else if (MLSTM && col == dv) v = 1.f;
     float keep = MLSTM ? 0.f : a.decay[h], m_new = 0.f;
     if (MLSTM) {
@@ -374,12 +377,14 @@ LQ_EXPORT int lq_linear_scan(const void* qkv, int dtype, int stride, int q_off, 
                              const float* sin_t, int rot, const int* tok_pos, const float* gate_pre,
                              const float* gate_bias, float gate_cap, const float* decay, float q_scale, float k_scale,
                              float* state, long long slot_stride, const int* cu_rows, const int* slots, float* out,
-                             float* exp_neg_m, int B, int H, int dk, int dv, int mlstm, int single, cudaStream_t stream) {
+                             float* exp_neg_m, int B, int H, int dk, int dv, int mlstm, int single, int in_act,
+                             cudaStream_t stream) {
     if (B <= 0) return LQ_OK;
+    if (in_act < 0 || in_act > 1) return LQ_BAD_SIZE;
     if (rot % 2 || rot > dk || (rot && (!cos_t || !sin_t))) return LQ_BAD_SIZE;
     if (mlstm ? (!gate_pre || !gate_bias || !exp_neg_m) : !decay) return LQ_BAD_SIZE;
     ScanArgs a{qkv, stride, q_off, k_off, v_off, cos_t, sin_t, rot, tok_pos, gate_pre, gate_bias, gate_cap, decay,
-               q_scale, k_scale, state, slot_stride, cu_rows, slots, out, exp_neg_m, H, dk, dv};
+               q_scale, k_scale, state, slot_stride, cu_rows, slots, out, exp_neg_m, H, dk, dv, in_act};
     if (single) {
         // Every sequence brings exactly one token (row cu_rows[b]).
         if (dk > 256) return LQ_BAD_SIZE;

@@ -349,11 +349,11 @@ def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: in
               T, n_rot, k_first, Hkv, hd, vd, v_off, page_size, _stream()), "rope_partial")
 
 
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "gelu": 4}
 
 
 def activation(x: torch.Tensor, kind: str, out: torch.Tensor | None = None) -> torch.Tensor:
-    """act(x) element by element, computed in float32: relu2 (the square of relu), gelu_tanh, silu, relu."""
+    """act(x) element by element, computed in float32: relu2 (the square of relu), gelu_tanh, silu, relu, gelu (the erf form)."""
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation {kind!r} is not one of {', '.join(ACTIVATIONS)}")
     if out is None:
@@ -383,18 +383,166 @@ def gate_mul(x: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch
     return x
 
 
+def gated_act(gu: torch.Tensor, bias: torch.Tensor | None, kind: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """gu [T, 2F] (gate columns, then up columns) -> act(gate + b_gate) * (up + b_up) [T, F]; bias float32 [2F] or None."""
+    T, F2 = gu.shape
+    F = F2 // 2
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} is not one of {', '.join(ACTIVATIONS)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != F2):
+        raise KernelError("gated_act: the bias must be float32 [2F]")
+    out = torch.empty((T, F), dtype=out_dtype, device=gu.device)
+    fn = _fn("plain_kernels", "lq_gated_act", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(gu, "gu")), dtype_code(gu), _p(bias), _p(out), dtype_code(out), T, F, ACTIVATIONS[kind], _stream()), "gated_act")
+    return out
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[t, :] += bias in place (float32 rows of the stream, float32 bias)."""
+    if x.dtype != torch.float32 or bias.dtype != torch.float32 or bias.numel() != x.shape[1]:
+        raise KernelError("add_bias works on float32 rows with a float32 bias of their width")
+    fn = _fn("plain_kernels", "lq_add_bias", [c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(bias), x.shape[0], x.shape[1], _stream()), "add_bias")
+    return x
+
+
+# ------------------------------------------------------------------ attention over a latent cache
+def latent_kv_store(rows: torch.Tensor, c_off: int, r_off: int, gain: torch.Tensor, eps: float, cos, sin, rot: int, tok_pos,
+                    tok_seq, slots, page_table, pages: torch.Tensor, R: int, dr: int, page_size: int) -> None:
+    """For every row: the latent (columns c_off .. c_off + R) over its root mean square times `gain`, and the shared key
+    part (columns r_off .. r_off + dr) with its first `rot` dimensions rotated by the row's position, stored as one row
+    [R + dr] of the row's cache page (pages [pages, page_size, R + dr])."""
+    if rows.stride(1) != 1 or gain.dtype != torch.float32 or gain.numel() != R:
+        raise KernelError("latent_kv_store: rows with unit column stride and a float32 gain [R]")
+    if pages.shape[-1] != R + dr or not pages.is_contiguous():
+        raise KernelError(f"latent_kv_store: cache rows must be {R + dr} wide")
+    if rot:
+        for t in (cos, sin):
+            if t is None or t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != rot // 2 or not t.is_contiguous():
+                raise KernelError(f"latent_kv_store: cos/sin tables must be contiguous float32 [positions, {rot // 2}]")
+    fn = _fn("latent_attn", "lq_latent_kv_store", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(rows), dtype_code(rows), rows.stride(0), c_off, r_off, _p(gain), float(eps), _p(cos), _p(sin), int(rot),
+              _p(tok_pos), _p(tok_seq), _p(slots), _p(page_table), page_table.stride(0), _p(pages), dtype_code(pages),
+              rows.shape[0], R, dr, page_size, _stream()), "latent_kv_store")
+
+
+def rope_tail(src: torch.Tensor, src_head: int, src_off: int, out: torch.Tensor, out_head: int, out_off: int, cos, sin,
+              rot: int, tok_pos, H: int, n: int) -> None:
+    """The n columns at src_off of each of the H heads (src_head wide) of src's rows, their first `rot` dimensions rotated
+    by the row's position, written to out (float32) at out_off of each head (out_head wide)."""
+    if src.stride(1) != 1 or out.stride(1) != 1 or out.dtype != torch.float32:
+        raise KernelError("rope_tail: unit column strides and a float32 output")
+    fn = _fn("latent_attn", "lq_rope_tail", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                             c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(src), dtype_code(src), src.stride(0), src_head, src_off, _p(out), out.stride(0), out_head, out_off, _p(cos),
+              _p(sin), int(rot), _p(tok_pos), src.shape[0], H, n, _stream()), "rope_tail")
+
+
+def head_matmul(src: torch.Tensor, src_head: int, src_off: int, w: torch.Tensor, out: torch.Tensor, out_head: int,
+                out_off: int) -> torch.Tensor:
+    """out[t, h * out_head + out_off + n] = sum_k src[t, h * src_head + src_off + k] * w[h, k, n] for w [H, K, N]: one small
+    matrix per head, float32 sums over k in rising order."""
+    H, K, N = w.shape
+    if src.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError("head_matmul: unit column strides and a contiguous weight [H, K, N]")
+    fn = _fn("latent_attn", "lq_head_matmul", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(src), dtype_code(src), src.stride(0), src_head, src_off, _p(w), dtype_code(w), _p(out), dtype_code(out),
+              out.stride(0), out_head, out_off, src.shape[0], H, K, N, _stream()), "head_matmul")
+    return out
+
+
+def latent_attention(q: torch.Tensor, pages: torch.Tensor, page_table, tok_pos, tok_seq, slots, H: int, R: int, page_size: int,
+                     scale: float, window: int | None, splits: int = 1) -> torch.Tensor:
+    """Causal attention of every row's H wide queries q [T, H, Dk] (float32) over the latent rows of its sequence's cache
+    (pages [pages, page_size, Dk]): scores over all Dk numbers, values the rows' first R numbers.  Returns float32
+    [T, H, R].  splits: slices that each row's keys are cut into (merged by a second kernel)."""
+    T, Hq, Dk = q.shape
+    if q.dtype != torch.float32 or not q.is_contiguous() or Hq != H or pages.shape[-1] != Dk or not pages.is_contiguous():
+        raise KernelError("latent_attention: contiguous float32 queries [T, H, Dk] and cache rows of Dk numbers")
+    if R > 512:
+        raise KernelError(f"latent_attention: a latent of {R} numbers exceeds 512")
+    out = torch.empty((T, H, R), dtype=torch.float32, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((T, H, splits, R), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T, H, splits, 2), dtype=torch.float32, device=q.device)
+    fn = _fn("latent_attn", "lq_latent_attention", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                    c_int, c_int, c_void_p])
+    _check(fn(_p(q), _p(pages), dtype_code(pages), _p(page_table), page_table.stride(0), _p(tok_pos), _p(tok_seq), _p(slots),
+              _p(out), _p(part_o), _p(part_ml), T, H, R, Dk, page_size, float(scale), int(window or 0), int(splits), _stream()),
+           "latent_attention", 2 if splits > 1 else 1, "latent_attention:slices" if splits > 1 else None)
+    return out
+
+
+# ------------------------------------------------------------------ routed feed-forward
+MOE_ACTS = {None: 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
+
+
+def moe_route(z: torch.Tensor, E: int, groups: int, keep: int, top: int, scale: float):
+    """Router logits z float32 [T, >= E] (the first E columns) -> (ids int32 [T, top], weights float32 [T, top]): sigmoid
+    scores; the `keep` best of `groups` equal groups of neighbouring experts by the sum of each group's two best scores;
+    of their experts the `top` best; weights = the chosen scores over their sum, times `scale`."""
+    T = z.shape[0]
+    if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < E:
+        raise KernelError("moe_route: float32 logits with unit column stride")
+    ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=z.device)
+    fn = _fn("moe", "lq_moe_route", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_p(z), z.stride(0), _p(ids), _p(weights), T, E, groups, keep, top, float(scale), _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: str | None) -> torch.Tensor:
+    """u[t, j] = act(w_up[ids[t, j]] h[t]) for w_up [E, F, D]; returns [T, top, F] in h's dtype."""
+    T, D = h.shape
+    E, F, D2 = w_up.shape
+    if D2 != D or w_up.dtype != h.dtype or not w_up.is_contiguous():
+        raise KernelError("moe_up: a contiguous weight [E, F, D] of the rows' dtype")
+    top = ids.shape[1]
+    u = torch.empty((T, top, F), dtype=h.dtype, device=h.device)
+    fn = _fn("moe", "lq_moe_up", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(h, "h")), _p(w_up), _p(ids), _p(u), dtype_code(h), T, top, D, F, MOE_ACTS[act], _stream()), "moe_up")
+    return u
+
+
+def moe_down(u: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor,
+             accumulate: bool = True, shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
+    """x[t] (+)= sum_j weights[t, j] w_down[ids[t, j]] u[t, j] (+ sigmoid(shared_gate[t]) * shared[t]) for w_down
+    [E, D, F]; x float32 [T, D]; shared float32 [T, D]; shared_gate float32 [T] (may be a strided column; None: the
+    shared rows are added as they are)."""
+    T, top, F = u.shape
+    E, D, F2 = w_down.shape
+    if F2 != F or w_down.dtype != u.dtype or not w_down.is_contiguous() or x.dtype != torch.float32 or tuple(x.shape) != (T, D):
+        raise KernelError("moe_down: a contiguous weight [E, D, F] of u's dtype and float32 rows [T, D]")
+    if shared is not None and (shared.dtype != torch.float32 or tuple(shared.shape) != (T, D) or not shared.is_contiguous()):
+        raise KernelError("moe_down: the shared rows must be contiguous float32 [T, D]")
+    if shared_gate is not None and (shared_gate.dtype != torch.float32 or shared_gate.numel() != T):
+        raise KernelError("moe_down: the shared gate must be float32 [T]")
+    fn = _fn("moe", "lq_moe_down", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                    c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(u, "u")), _p(w_down), _p(ids), _p(weights), _p(shared), _p(shared_gate),
+              shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), dtype_code(u),
+              T, top, D, F, _stream()), "moe_down")
+    return x
+
+
 # ------------------------------------------------------------------ mixers with a matrix state per head
 def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, cu_rows, slots, tok_pos,
                 B: int, H: int, dk: int, dv: int, q_scale: float = 1.0, k_scale: float = 1.0,
                 decay: torch.Tensor | None = None, gates: tuple | None = None, rot: tuple | None = None,
-                single: bool = False):
+                single: bool = False, in_act: str | None = None):
     """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t for the rows of B sequences (rows cu_rows[b] ..
     cu_rows[b+1] of qkv belong to the sequence in slot slots[b]), from and into `state` (float32
     [slots, H, dk (+1), dv (+1)]).  decay: float32 [H] (a_t fixed, b_t = 1).  gates = (pre [rows, 2H] float32,
     bias [2H] float32, cap): exponential input gate and sigmoid forget gate with a running maximum; the state then
     has one more row (the maximum) and one more column (the normaliser).  rot = (cos, sin, dims): q and k are
     rotated as they are read.  single: every sequence brings exactly one token (the kernel then streams the
-    state once, without staging chunks of tokens).  Returns the raw outputs float32 [rows, H, dv (+1)] and,
+    state once, without staging chunks of tokens).  in_act "silu": q, k and v each pass through silu, in float32, as
+    they are read.  Returns the raw outputs float32 [rows, H, dv (+1)] and,
     with gates, exp(-maximum) float32 [rows, H]."""
     rows = qkv.shape[0]
     mlstm = gates is not None
@@ -419,10 +567,11 @@ def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
     fn = _fn("recurrent", "lq_linear_scan", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_float, c_void_p,
                                              c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                             c_int, c_int, c_void_p])
+                                             c_int, c_int, c_int, c_void_p])
     _check(fn(_p(qkv), dtype_code(qkv), qkv.stride(0), q_off, k_off, v_off, _p(cos), _p(sin), int(dims), _p(tok_pos),
               _p(pre), _p(bias), float(cap), _p(decay), float(q_scale), float(k_scale), _p(state), state.stride(0),
-              _p(cu_rows), _p(slots), _p(out), _p(enm), B, H, dk, dv, int(mlstm), int(single and rows == B), _stream()),
+              _p(cu_rows), _p(slots), _p(out), _p(enm), B, H, dk, dv, int(mlstm), int(single and rows == B),
+              {None: 0, "silu": 1}[in_act], _stream()),
            "linear_scan", 1, "linear_scan:single" if single and rows == B else None)
     return out, enm
 

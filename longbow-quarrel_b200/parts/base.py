@@ -125,12 +125,13 @@ class KVNeed(CacheNeed):
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None        # values of another size than the keys
+    values: bool = True                  # False: no pool of values (a mixer whose values are a part of its keys' rows)
 
     def make_group(self, entries, sizing):
         from ..cache.paged import PagedKVGroup
         return PagedKVGroup(entries, self.n_kv_heads, self.head_dim, self.window, sizing.n_pages, sizing.page_size,
                             sizing.max_slots, sizing.pages_per_seq, sizing.dtype, sizing.device,
-                            v_head_dim=self.v_head_dim)
+                            v_head_dim=self.v_head_dim, values=self.values)
 
 
 @dataclass(frozen=True)

@@ -1,6 +1,7 @@
 """The arrangement of parts in a layer.
 
-"pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)), the order of the reference's
+"pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)) (norm2 and ffn together, or a layer of a mixer
+alone), the order of the reference's
 block (internal/device/metal.go:1347-1527), with the residual stream x in 32-bit
 throughout (internal/engine/engine.go:1375).
 
@@ -22,13 +23,16 @@ class PreNormBlock(Part):
         unknown = set(layer.parts) - {"norm1", "mixer", "norm2", "ffn"}
         if unknown:
             raise ValueError(f"layer {layer.prefix!r}: the arrangement 'pre_norm' has no place {sorted(unknown)}")
+        if len(set(layer.parts) & {"norm2", "ffn"}) == 1:
+            raise ValueError(f"layer {layer.prefix!r}: norm2 and ffn come together or not at all")
         self.norm1 = make_part("norm", layer.part("norm1"), runtime)
         self.mixer = make_part("mixer", layer.part("mixer"), runtime)
-        self.norm2 = make_part("norm", layer.part("norm2"), runtime)
-        self.ffn = make_part("ffn", layer.part("ffn"), runtime)
+        self.has_ffn = "ffn" in layer.parts
+        self.norm2 = make_part("norm", layer.part("norm2"), runtime) if self.has_ffn else None
+        self.ffn = make_part("ffn", layer.part("ffn"), runtime) if self.has_ffn else None
 
     def parts(self):
-        return (self.norm1, self.mixer, self.norm2, self.ffn)
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None)
 
     def cache_need(self):
         """What the layer's cache entry must hold: its mixer's need."""
@@ -69,6 +73,11 @@ class PreNormBlock(Part):
         input_norm() of the layer that follows.  Returns that layer's rows, or None."""
         n_rows = x.shape[0]
         h = normed if normed is not None else self.norm1.forward(x)
+        if not self.has_ffn:
+            if emit is not None and self.mixer.folds_norm:
+                return self.mixer.forward(h, ctx, cache_view, x, writes_cache, emit=emit)
+            self.mixer.forward(h, ctx, cache_view, x, writes_cache)
+            return None
         fold2 = self.norm2.foldable(n_rows) if (self.mixer.folds_norm and self.ffn.folds_norm) else None
         h = self.mixer.forward(h, ctx, cache_view, x, writes_cache, emit=fold2) if fold2 is not None \
             else self.mixer.forward(h, ctx, cache_view, x, writes_cache)

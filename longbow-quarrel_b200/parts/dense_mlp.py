@@ -1,5 +1,5 @@
 """Feed-forward without a gate: y = W_down act(W_up h), act one of `kernels.ops.ACTIVATIONS`
-(relu2: the square of relu; gelu_tanh; silu; relu)."""
+(relu2: the square of relu; gelu_tanh; gelu, the erf form; silu; relu)."""
 from __future__ import annotations
 
 import torch

@@ -1,0 +1,86 @@
+"""Feed-forward of many small experts, of which each token uses a few.
+
+    z = W_router h (32-bit)        s = sigmoid(z)
+    experts form `groups` equal groups of neighbours; a group's score is the sum of its two largest s;
+    only experts of the `keep` best groups can be chosen; of those, the `top` with the largest s are
+    g_e = s_e / (sum of the chosen s + 1e-20) * route_scale
+    y = sum_e g_e W_down,e act(W_up,e h)  [ + sigmoid(w_sg . h) * shared(h) ]
+
+The experts have no gate and no bias.  A shared expert (a `dense_mlp` of its own size) runs for every
+token behind one sigmoid number per token.  The router's logits and the shared expert's gate come
+from one 32-bit product; choice and weights are one kernel, the experts' two products one kernel
+each (`csrc/moe.cu`), the second of which also adds the shared expert's rows and joins the stream.
+Every kernel reads the chosen experts from device memory, so a step can be captured and replayed.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.spec import WeightSpec
+from .base import FeedForward, Runtime, StepContext
+from .registry import make_part, register_part
+from .spec import PartSpec
+
+
+@register_part("ffn", "routed_experts")
+class RoutedExperts(FeedForward):
+    graph_safe = True
+    kernel_libraries = ("moe", "recurrent")          # `recurrent` holds the 32-bit product for weights of few rows
+
+    def __init__(self, runtime: Runtime, hidden_size: int, n_experts: int, top: int, expert_size: int,
+                 activation: str = "gelu", groups: int = 1, keep_groups: int = 1, route_scale: float = 1.0,
+                 shared_size: int | None = None, shared_activation: str | None = None, names: dict | None = None):
+        if activation not in ops.MOE_ACTS:
+            raise ValueError(f"routed_experts: activation {activation!r} is not one of {', '.join(map(str, ops.MOE_ACTS))}")
+        if n_experts % groups or not 1 <= keep_groups <= groups:
+            raise ValueError(f"routed_experts: {n_experts} experts in {groups} groups, {keep_groups} kept")
+        if not 1 <= top <= keep_groups * (n_experts // groups):
+            raise ValueError(f"routed_experts: {top} experts per token, but only {keep_groups * (n_experts // groups)} can be chosen")
+        self.runtime, self.D, self.E, self.top, self.F = runtime, hidden_size, n_experts, top, expert_size
+        self.activation, self.groups, self.keep, self.route_scale = activation, groups, keep_groups, float(route_scale)
+        self.names = {"router": "router", "expert": "e{}", "up": "up", "down": "down", "shared": "shared", "shared_gate": "shared.sg",
+                      **(names or {})}
+        self.shared = None
+        if shared_size:
+            n = self.names
+            self.shared = make_part("ffn", PartSpec("dense_mlp", {
+                "hidden_size": hidden_size, "intermediate_size": shared_size, "activation": shared_activation or activation,
+                "names": {"up": f"{n['shared']}.{n['up']}", "down": f"{n['shared']}.{n['down']}"}}), runtime)
+        self.w_route = self.w_up = self.w_down = None
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.names['expert'].format(e)}.{self.names[which]}"
+
+    def weights(self):
+        out = {self.names["router"]: WeightSpec((self.E, self.D))}
+        for e in range(self.E):
+            out[self._expert(e, "up")] = WeightSpec((self.F, self.D))
+            out[self._expert(e, "down")] = WeightSpec((self.D, self.F))
+        if self.shared is not None:
+            out.update(self.shared.weights())
+            out[self.names["shared_gate"]] = WeightSpec((1, self.D))
+        return out
+
+    def load(self, tensors):
+        rows = [tensors[self.names["router"]]] + ([tensors[self.names["shared_gate"]]] if self.shared is not None else [])
+        self.w_route = torch.cat(rows, dim=0).contiguous()           # the shared expert's gate rides behind the router's rows
+        self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous()
+        if self.w_up.dtype != self.runtime.act_dtype:
+            # The experts' kernels read rows and weights of one dtype.
+            self.w_up, self.w_down = self.w_up.to(self.runtime.act_dtype), self.w_down.to(self.runtime.act_dtype)
+        if self.shared is not None:
+            self.shared.load({name: tensors[name] for name in self.shared.weights()})
+
+    def forward(self, h, ctx: StepContext, residual):
+        z = ops.small_proj(h, self.w_route)                          # float32 [T, E (+ 1)]
+        ids, weights = ops.moe_route(z, self.E, self.groups, self.keep, self.top, self.route_scale)
+        u = ops.moe_up(h, self.w_up, ids, self.activation)
+        shared = self.shared.forward(h, ctx, None) if self.shared is not None else None
+        gate = z[:, self.E] if self.shared is not None else None
+        if residual is None:
+            out = torch.empty((h.shape[0], self.D), dtype=torch.float32, device=h.device)
+            return ops.moe_down(u, self.w_down, ids, weights, out, accumulate=False, shared=shared, shared_gate=gate)
+        ops.moe_down(u, self.w_down, ids, weights, residual, accumulate=True, shared=shared, shared_gate=gate)
+        return None

@@ -17,6 +17,10 @@ fixed-size state of the sequence's slot, which is zero when a sequence starts:
              Output: each head over its root mean square, times a weight, times sigmoid(W_g h),
              then W_o.
 
+"lightning"  a_t = the head's fixed decay, b_t = 1; q, k and v each pass through silu; no rotation and no
+             scale.  Output: all heads together over their root mean square, times a weight, times
+             sigmoid(W_g h), then W_o.
+
 Gates, decays, the state and the per-head norms are 32-bit in both precisions; the
 gates' pre-activations come from a 32-bit product of their own.  A sequence's tokens
 are walked in order from the state in its slot (`csrc/recurrent.cu`: one kernel for
@@ -100,6 +104,40 @@ class Retention(_MatrixStateMixer):
                                  H, dk, dv, k_scale=dk ** -0.5, decay=self.decay, rot=rot, single=ctx.decode)
         g_off = 2 * H * dk + H * dv
         out = ops.head_norm_gate(raw, dv, self.eps, self.runtime.act_dtype, gate=rows[:, g_off:g_off + H * dv], act="silu")
+        return self._finish(out, residual)
+
+
+@register_part("mixer", "lightning")
+class Lightning(_MatrixStateMixer):
+    def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, key_dim: int, value_dim: int, decay, eps: float,
+                 names: dict | None = None):
+        super().__init__(runtime, hidden_size, n_heads, key_dim, value_dim, eps, {"norm": "norm", **(names or {})})
+        if len(decay) != n_heads:
+            raise ValueError(f"lightning: {len(decay)} decays for {n_heads} heads")
+        self.decay_values = tuple(float(d) for d in decay)
+        self.decay = self.norm_weight = None
+
+    def cache_need(self):
+        return StateNeed((self.H, self.dk, self.dv), torch.float32)
+
+    def weights(self):
+        return {**self._base_weights(), self.names["norm"]: WeightSpec((self.H * self.dv,), init="gain", full_precision=True)}
+
+    def load(self, tensors):
+        self._load_base(tensors)
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.runtime.device)
+        self.norm_weight = tensors[self.names["norm"]].to(torch.float32).contiguous()
+
+    def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
+        H, dk, dv = self.H, self.dk, self.dv
+        rows = linear.linear(h, self.w_in, self.runtime.act_dtype)
+        # silu meets q, k and v in 32-bit as the scan reads them: nothing that enters the recurrence is rounded again.
+        raw, _ = ops.linear_scan(rows, 0, H * dk, 2 * H * dk, cache_view, ctx.cu_rows, ctx.slots, ctx.tok_pos, ctx.B,
+                                 H, dk, dv, decay=self.decay, single=ctx.decode, in_act="silu")
+        g_off = 2 * H * dk + H * dv
+        # One norm over all heads: the heads' outputs as a single "head" of H * dv numbers.
+        out = ops.head_norm_gate(raw.view(raw.shape[0], 1, H * dv), H * dv, self.eps, self.runtime.act_dtype,
+                                 weight=self.norm_weight, gate=rows[:, g_off:g_off + H * dv], act="sigmoid")
         return self._finish(out, residual)
 
 
