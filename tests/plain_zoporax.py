@@ -103,7 +103,7 @@ def rotate(x: torch.Tensor, pos: int, freqs: torch.Tensor, mult: float) -> torch
     """x [..., dims]: dimension i pairs with i + dims / 2."""
     half = freqs.numel()
     a = pos * freqs
-    c, s = torch.cos(a) * mult, torch.sin(a) * mult
+    c, s = (torch.cos(a) * mult).to(x.dtype), (torch.sin(a) * mult).to(x.dtype)
     u, v = x[..., :half], x[..., half:2 * half]
     return torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], dim=-1)
 
@@ -165,6 +165,28 @@ def expert(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tenso
     return _st(gelu_erf(_st(h @ up.T))) @ down.T
 
 
+_MARGINS = None        # set by forward(margins_out=...): receives, per routed layer, every token's narrowest choice
+
+
+def choice_margin(scores: torch.Tensor, router: dict) -> float:
+    """How far the token's choice is from another one: the smallest gap, in score, between what was just taken and
+    what was just left (the last kept and the first dropped group, by the groups' scores; the last chosen and the
+    first unchosen expert of the kept groups).  Infinite when nothing is left out."""
+    E, top = router["experts"], router["top"]
+    groups = router.get("groups") or {"count": 1, "keep": 1}
+    per = E // groups["count"]
+    margin = float("inf")
+    group_score = scores.reshape(groups["count"], per).topk(min(2, per), dim=1).values.sum(dim=1)
+    ranked = group_score.sort(descending=True)
+    if groups["keep"] < groups["count"]:
+        margin = float(ranked.values[groups["keep"] - 1] - ranked.values[groups["keep"]])
+    kept = ranked.indices[:groups["keep"]].tolist()
+    inside = torch.cat([scores[g * per:(g + 1) * per] for g in kept]).sort(descending=True).values
+    if top < inside.numel():
+        margin = min(margin, float(inside[top - 1] - inside[top]))
+    return margin
+
+
 def route(scores: torch.Tensor, router: dict) -> tuple[list[int], torch.Tensor]:
     """scores [E] of one token -> (chosen experts, their weights)."""
     E, top = router["experts"], router["top"]
@@ -187,6 +209,8 @@ def routed_ffn(h: torch.Tensor, w: dict, mlp: dict) -> torch.Tensor:
     T = h.shape[0]
     out = torch.zeros(T, w["e0.down"].shape[0], dtype=h.dtype)
     scores = torch.sigmoid(h @ w["router"].T)
+    if _MARGINS is not None:
+        _MARGINS.append(torch.tensor([choice_margin(scores[t], router) for t in range(T)], dtype=torch.float64))
     for t in range(T):
         chosen, weights = route(scores[t], router)
         for e, g in zip(chosen, weights):
@@ -202,11 +226,13 @@ def _sub(weights: dict, prefix: str, dtype) -> dict:
     return {k[len(prefix):]: v.to(dtype) for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, storage=None, layers_out: list | None = None) -> torch.Tensor:
+def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, storage=None, layers_out: list | None = None,
+            margins_out: list | None = None) -> torch.Tensor:
     """Logits [T, vocab] of one sequence.  storage: keep activations in this dtype between operations (everything
-    else stays in `dtype`).  layers_out: receives the residual stream after every layer."""
-    global _STORAGE
-    _STORAGE = storage
+    else stays in `dtype`).  layers_out: receives the residual stream after every layer.  margins_out: receives, for
+    every routed layer, each token's `choice_margin`."""
+    global _STORAGE, _MARGINS
+    _STORAGE, _MARGINS = storage, margins_out
     try:
         eps = cfg["norm"]["eps"]
         embed = weights["embed"].to(dtype)
@@ -230,4 +256,11 @@ def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, storage=None,
                 layers_out.append(x.clone())
         return _st(rms_norm(x, weights["final.norm"].to(dtype), eps)) @ embed.T
     finally:
-        _STORAGE = None
+        _STORAGE = _MARGINS = None
+
+
+def greedy(cfg: dict, weights: dict, prompt, n_new: int) -> list[int]:
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(forward(cfg, weights, seq)[-1].argmax()))
+    return seq[len(prompt):]

@@ -1,0 +1,320 @@
+"""The kernels that the Zoporax design added, each alone against a float64 restatement of its own operation
+written here: the latent cache write, the rotation of a head's tail, per-head matrices, attention over latent
+rows (window edges, page borders, a far key, the first tokens, shuffled pages with NaN elsewhere, sliced keys),
+the router, the experts' products, the gated activation, and the scan with silu on its inputs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from longbow_quarrel_b200.kernels import ops
+    return ops
+
+
+def _i32(values):
+    return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+
+def _tables(dims, n_pos, base=100.0, mult=1.0):
+    f = torch.tensor(base, dtype=torch.float64) ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / dims)
+    a = torch.arange(n_pos, dtype=torch.float64)[:, None] * f
+    return (torch.cos(a) * mult).float().to(DEV).contiguous(), (torch.sin(a) * mult).float().to(DEV).contiguous()
+
+
+def _rotate(x, pos, cos, sin, rot):
+    """float64 reference: x [..., n], first `rot` dimensions rotated by the tables' row `pos`."""
+    half = rot // 2
+    c, s = cos[pos].double().cpu(), sin[pos].double().cpu()
+    u, v = x[..., :half], x[..., half:rot]
+    return torch.cat([u * c - v * s, v * c + u * s, x[..., rot:]], dim=-1)
+
+
+def _rel(got, ref):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return float((got - ref).norm() / ref.norm().clamp_min(1e-30))
+
+
+# ------------------------------------------------------------------ cache write, rotation, per-head matrices
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,dr,rot", [(24, 8, 8), (20, 12, 8), (96, 24, 24), (36, 4, 0)])
+def test_latent_rows_are_normed_rotated_and_stored_in_their_pages(dtype, R, dr, rot):
+    ops = _ops()
+    g = torch.Generator().manual_seed(R)
+    page_size, T = 8, 13
+    rows = torch.randn(T, 5 + R + dr + 3, generator=g)
+    gain = (1 + 0.3 * torch.randn(R, generator=g)).float()
+    cos, sin = _tables(rot, 64) if rot else (None, None)
+    # Two sequences in slots 2 and 0: positions 5..11 of one, 0..5 of the other, pages handed out in a shuffled order.
+    pos = list(range(5, 12)) + list(range(0, 6))
+    seq = [0] * 7 + [1] * 6
+    table = torch.full((3, 4), -1, dtype=torch.int32)
+    table[2, :2] = torch.tensor([3, 1])
+    table[0, :1] = torch.tensor([4])
+    pages = torch.full((6, page_size, R + dr), float("nan"), dtype=dtype, device=DEV)
+    ops.latent_kv_store(rows.to(DEV), 5, 5 + R, gain.to(DEV), 1e-5, cos, sin, rot, _i32(pos), _i32(seq), _i32([2, 0]),
+                        table.to(DEV), pages, R, dr, page_size)
+    got = pages.float().cpu()
+    x = rows.double()
+    written = set()
+    for t in range(T):
+        c = x[t, 5:5 + R]
+        ref = torch.cat([c / torch.sqrt((c * c).mean() + 1e-5) * gain.double(),
+                         _rotate(x[t, 5 + R:5 + R + dr], pos[t], cos, sin, rot) if rot else x[t, 5 + R:5 + R + dr]])
+        page = int(table[[2, 0][seq[t]], pos[t] // page_size])
+        written.add((page, pos[t] % page_size))
+        assert _rel(got[page, pos[t] % page_size], ref) < (1e-6 if dtype == torch.float32 else 4e-3), t
+    untouched = [(p, r) for p in range(6) for r in range(page_size) if (p, r) not in written]
+    assert all(torch.isnan(got[p, r]).all() for p, r in untouched)
+
+
+@pytest.mark.parametrize("src_dtype", [torch.float32, torch.bfloat16])
+def test_the_tail_of_every_head_is_rotated_into_the_wide_query(src_dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    T, H, dn, dr, R, rot = 9, 3, 10, 12, 7, 8
+    q = torch.randn(T, H * (dn + dr), generator=g).to(src_dtype)
+    cos, sin = _tables(rot, 300, mult=1.07)
+    pos = [0, 1, 2, 100, 101, 299, 7, 8, 9]
+    wide = torch.zeros(T, H * (R + dr), device=DEV)
+    ops.rope_tail(q.to(DEV), dn + dr, dn, wide, R + dr, R, cos, sin, rot, _i32(pos), H, dr)
+    qd = q.double().reshape(T, H, dn + dr)
+    for t in range(T):
+        ref = _rotate(qd[t, :, dn:], pos[t], cos, sin, rot)
+        assert _rel(wide[t].reshape(H, R + dr)[:, R:], ref) < 1e-6
+    assert float(wide.reshape(T, H, R + dr)[:, :, :R].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("in_dtype,w_dtype,out_dtype", [(torch.float32, torch.float32, torch.float32),
+                                                        (torch.float32, torch.bfloat16, torch.float32),
+                                                        (torch.float32, torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("T,H,K,N", [(1, 1, 8, 5), (13, 3, 24, 40), (70, 8, 32, 96), (9, 2, 300, 17)])
+def test_one_matrix_per_head(in_dtype, w_dtype, out_dtype, T, H, K, N):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + K)
+    src = torch.randn(T, H * (K + 3) + 2, generator=g).to(in_dtype)
+    w = (torch.randn(H, K, N, generator=g) / math.sqrt(K)).to(w_dtype)
+    out = torch.full((T, H * (N + 4)), 7.0, dtype=out_dtype, device=DEV)
+    ops.head_matmul(src.to(DEV), K + 3, 2, w.to(DEV), out, N + 4, 1)
+    ref = torch.einsum("thk,hkn->thn", src.double()[:, :H * (K + 3)].reshape(T, H, K + 3)[:, :, 2:2 + K], w.double())
+    got = out.reshape(T, H, N + 4)
+    assert _rel(got[:, :, 1:1 + N], ref) < (2e-6 if out_dtype == torch.float32 else 4e-3)
+    assert (got[:, :, 0] == 7.0).all() and (got[:, :, 1 + N:] == 7.0).all()          # nothing beside its columns
+
+
+# ------------------------------------------------------------------ the attention
+
+def _latent_reference(q, rows, pos, window, R, scale):
+    """q [H, Dk] float64, rows [n, Dk] the sequence's latent rows: softmax over the window, mean of the rows' first R."""
+    first = 0 if not window else max(0, pos - window + 1)
+    keys = rows[first:pos + 1]
+    p = torch.softmax(keys @ q.T * scale, dim=0)            # [keys, H]
+    return p.T @ keys[:, :R]
+
+
+def _paged(rows_by_seq, Dk, page_size, dtype, n_pages, seed):
+    """The sequences' rows laid into pages in a shuffled order, NaN everywhere else; returns (pages, table)."""
+    order = np.random.default_rng(seed).permutation(n_pages).tolist()
+    pages = torch.full((n_pages, page_size, Dk), float("nan"), dtype=dtype)
+    most = max(-(-len(r) // page_size) for r in rows_by_seq.values())
+    table = torch.full((max(rows_by_seq) + 1, most), -1, dtype=torch.int32)
+    for slot, rows in rows_by_seq.items():
+        for p in range(-(-len(rows) // page_size)):
+            page = order.pop()
+            table[slot, p] = page
+            chunk = rows[p * page_size:(p + 1) * page_size]
+            pages[page, :len(chunk)] = chunk.to(dtype)
+    return pages.to(DEV), table.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,R,dr,window,splits", [(3, 24, 8, 33, 1), (1, 20, 12, None, 1), (8, 96, 24, 64, 1), (9, 40, 16, 100, 3),
+                                                  (2, 300, 20, 5, 1), (4, 16, 8, 64, 4)])
+def test_attention_over_latent_rows(dtype, H, R, dr, window, splits):
+    """Rows of three sequences in one launch: whole prompts from the first token, positions on both sides of page
+    borders and of the window's edge, and single late rows."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(H * 100 + R)
+    Dk, page_size = R + dr, 16
+    lens = {0: 150, 2: 70, 3: 17}
+    rows = {s: torch.randn(n, Dk, generator=g) for s, n in lens.items()}
+    pages, table = _paged(rows, Dk, page_size, dtype, 20, seed=H)
+    stored = {s: r.to(dtype).double() for s, r in rows.items()}
+    slots = [2, 0, 3]
+    w = window or 0
+    # sequence 0 of the step (slot 2): its whole prompt; sequence 1 (slot 0): late rows around borders and the window; sequence 2: its last
+    pos = list(range(70)) + [15, 16, 17, 31, 32, 47, 48, 63, 64, 65, 99, 100, 101, 127, 128, 149] + [16]
+    seq = [0] * 70 + [1] * 16 + [2]
+    if w:
+        pos += [w - 2, w - 1, w, w + 1]
+        seq += [1] * 4
+    T = len(pos)
+    q = torch.randn(T, H, Dk, generator=g)
+    out = ops.latent_attention(q.to(DEV), pages, table, _i32(pos), _i32(seq), _i32(slots), H, R, page_size, 0.2, window, splits)
+    tol = 3e-6 if dtype == torch.float32 else 3e-6          # the reference reads the rounded cache rows: only sums differ
+    for t in range(T):
+        ref = _latent_reference(q[t].double(), stored[slots[seq[t]]], pos[t], w, R, 0.2)
+        assert _rel(out[t], ref) < tol, (t, pos[t], seq[t])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [40, 64, 257])
+@pytest.mark.parametrize("splits", [1, 5])
+def test_a_key_that_outweighs_all_others_just_inside_and_just_outside_the_window(dtype, window, splits):
+    """One cached row is made to match the query a hundred times better than the rest.  At the last position that
+    still sees it the output must be that row; one position later nothing of it may be left; and a row far back
+    (hundreds of keys away, across many pages) is found whole when there is no window."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(window)
+    H, R, dr, page_size = 2, 32, 8, 64
+    Dk = R + dr
+    n = 700
+    rows = 0.1 * torch.randn(n, Dk, generator=g)
+    planted = 300
+    direction = torch.randn(Dk, generator=g)
+    direction /= direction.norm()
+    rows[planted] = 8.0 * direction
+    pages, table = _paged({1: rows}, Dk, page_size, dtype, 12, seed=window)
+    stored = rows.to(dtype).double()
+    pos = [planted, planted + 1, planted + window - 2, planted + window - 1, planted + window, planted + window + 1, n - 1]
+    q = (8.0 * direction).repeat(len(pos), H, 1)
+    for win in (window, None):
+        out = ops.latent_attention(q.to(DEV), pages, table, _i32(pos), _i32([0] * len(pos)), _i32([1]), H, R, page_size, 1.0,
+                                   win, splits)
+        for t, p in enumerate(pos):
+            ref = _latent_reference(q[t].double(), stored, p, win or 0, R, 1.0)
+            assert _rel(out[t], ref) < 1e-5, (win, p)
+            sees = win is None or p - planted < win
+            closeness = _rel(out[t, 0], stored[planted, :R])
+            assert (closeness < 1e-3) == sees, (win, p, closeness)
+
+
+# ------------------------------------------------------------------ routed experts
+
+def _route_reference(z, E, groups, keep, top, scale):
+    s = torch.sigmoid(z.double())
+    per = E // groups
+    gs = s.reshape(groups, per).topk(min(2, per), dim=1).values.sum(dim=1)
+    allowed = torch.zeros(E, dtype=torch.bool)
+    for gidx in gs.topk(keep).indices.tolist():
+        allowed[gidx * per:(gidx + 1) * per] = True
+    chosen = torch.where(allowed, s, torch.full_like(s, -1.0)).topk(top).indices
+    return chosen.tolist(), (s[chosen] / (s[chosen].sum() + 1e-20) * scale)
+
+
+@pytest.mark.parametrize("E,groups,keep,top", [(8, 4, 1, 2), (6, 3, 2, 2), (16, 4, 2, 3), (5, 1, 1, 2), (3, 1, 1, 3), (64, 8, 3, 6),
+                                               (4, 4, 2, 1), (160, 8, 3, 6)])
+def test_the_router_chooses_by_groups(E, groups, keep, top):
+    ops = _ops()
+    g = torch.Generator().manual_seed(E * 10 + top)
+    T = 50
+    z = 2.0 * torch.randn(T, E + 1, generator=g)          # one more column rides along (another gate's logit)
+    ids, weights = ops.moe_route(z.to(DEV), E, groups, keep, top, 1.7)
+    ids, weights = ids.cpu(), weights.double().cpu()
+    for t in range(T):
+        chosen, ref = _route_reference(z[t, :E], E, groups, keep, top, 1.7)
+        assert ids[t].tolist() == chosen, t                  # in the order of their scores
+        assert (weights[t] - ref).abs().max() < 1e-6
+
+
+def test_the_router_leaves_the_best_expert_when_its_group_loses():
+    ops = _ops()
+    s = torch.tensor([[0.95, 0.05, 0.6, 0.55, 0.1, 0.2]])
+    z = torch.log(s / (1 - s))
+    ids, weights = ops.moe_route(z.to(DEV), 6, 3, 1, 2, 2.0)
+    assert sorted(ids[0].tolist()) == [2, 3] and float(weights.sum()) == pytest.approx(2.0, rel=1e-6)
+    ids, _ = ops.moe_route(z.to(DEV), 6, 3, 2, 2, 2.0)
+    assert sorted(ids[0].tolist()) == [0, 2]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,top,D,F", [(1, 3, 3, 40, 16), (37, 8, 2, 64, 24), (5, 16, 3, 100, 50), (300, 6, 1, 128, 48)])
+def test_the_experts_products_and_the_shared_rows_join_the_stream(dtype, T, E, top, D, F):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + E)
+    h = torch.randn(T, D, generator=g).to(dtype)
+    w_up = (torch.randn(E, F, D, generator=g) / math.sqrt(D)).to(dtype)
+    w_down = (torch.randn(E, D, F, generator=g) / math.sqrt(F)).to(dtype)
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    weights = torch.rand(T, top, generator=g)
+    shared = torch.randn(T, D, generator=g)
+    zs = torch.randn(T, 3, generator=g)
+    x0 = torch.randn(T, D, generator=g)
+    u = ops.moe_up(h.to(DEV), w_up.to(DEV), ids.to(DEV), "gelu")
+    pre = torch.einsum("tjfd,td->tjf", w_up.double()[ids.long()], h.double())
+    u_ref = 0.5 * pre * (1 + torch.erf(pre / math.sqrt(2.0)))
+    assert _rel(u, u_ref) < (2e-6 if dtype == torch.float32 else 4e-3)
+    x = x0.clone().to(DEV)
+    ops.moe_down(u, w_down.to(DEV), ids.to(DEV), weights.to(DEV), x, True, shared.to(DEV), zs.to(DEV)[:, 1])
+    y = torch.einsum("tjdf,tjf->tjd", w_down.double()[ids.long()], u.double().cpu())
+    ref = x0.double() + (weights.double()[:, :, None] * y).sum(1) + torch.sigmoid(zs[:, 1].double())[:, None] * shared.double()
+    assert _rel(x, ref) < 2e-6
+    out = torch.empty(T, D, device=DEV)
+    ops.moe_down(u, w_down.to(DEV), ids.to(DEV), weights.to(DEV), out, False)
+    assert _rel(out, (weights.double()[:, :, None] * y).sum(1)) < 2e-6
+
+
+# ------------------------------------------------------------------ element by element
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                                (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("kind", ["gelu_tanh", "gelu", "silu"])
+def test_gated_activation_with_biases(in_dtype, out_dtype, kind):
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    T, F = 11, 50
+    gu = (2 * torch.randn(T, 2 * F, generator=g)).to(in_dtype)
+    bias = torch.randn(2 * F, generator=g)
+    acts = {"gelu_tanh": lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))),
+            "gelu": lambda z: 0.5 * z * (1 + torch.erf(z / math.sqrt(2.0))), "silu": lambda z: z * torch.sigmoid(z)}
+    for b in (bias, None):
+        out = ops.gated_act(gu.to(DEV), b.to(DEV) if b is not None else None, kind, out_dtype)
+        x = gu.double() + (b.double() if b is not None else 0.0)
+        ref = acts[kind](x[:, :F]) * x[:, F:]
+        assert _rel(out, ref) < (2e-6 if out_dtype == torch.float32 else 4e-3)
+    x = torch.randn(T, F, generator=g)
+    got = ops.add_bias(x.clone().to(DEV), bias[:F].to(DEV))
+    assert _rel(got, x.double() + bias[:F].double()) < 1e-7
+    y = torch.randn(T, F, generator=g).to(in_dtype)
+    assert _rel(ops.activation(y.to(DEV), "gelu"), acts["gelu"](y.double())) < (2e-6 if in_dtype == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dk,dv", [(2, 16, 24), (1, 40, 12), (4, 64, 64)])
+def test_the_scan_with_silu_on_its_inputs_in_pieces_and_single_tokens(dtype, H, dk, dv):
+    """S_t = g S_(t-1) + silu(k_t) silu(v_t)^T, o_t = S_t^T silu(q_t): a prompt in one piece, in pieces of 2, 1, 30 and
+    the rest, and token by token, from a first token that must last (decay one on the last head)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(dk)
+    n = 90
+    rows = torch.randn(n, 2 * H * dk + H * dv + 5, generator=g).to(dtype)
+    rows[0] *= 4.0
+    decay = torch.tensor([0.9, 0.97, 0.5, 1.0][-H:], dtype=torch.float32)
+    x = rows.double()
+    act = lambda z: z * torch.sigmoid(z)
+    q = act(x[:, :H * dk]).reshape(n, H, dk)
+    k = act(x[:, H * dk:2 * H * dk]).reshape(n, H, dk)
+    v = act(x[:, 2 * H * dk:2 * H * dk + H * dv]).reshape(n, H, dv)
+    S = torch.zeros(H, dk, dv, dtype=torch.float64)
+    ref = torch.zeros(n, H, dv, dtype=torch.float64)
+    for t in range(n):
+        S = decay.double()[:, None, None] * S + k[t, :, :, None] * v[t, :, None, :]
+        ref[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    dev_rows = rows.to(DEV)
+    for pieces in ([n], [2, 1, 30, n - 33], [1] * n):
+        state = torch.zeros(3, H, dk, dv, device=DEV)
+        got, at = [], 0
+        for m in pieces:
+            out, _ = ops.linear_scan(dev_rows[at:at + m], 0, H * dk, 2 * H * dk, state, _i32([0, m]), _i32([1]),
+                                     _i32(list(range(at, at + m))), 1, H, dk, dv, decay=decay.to(DEV), single=(m == 1), in_act="silu")
+            got.append(out)
+            at += m
+        assert _rel(torch.cat(got), ref) < 1e-5, pieces[:3]
+        assert _rel(state[1], S) < 1e-5 and float(state[0].abs().max()) == 0.0
