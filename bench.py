@@ -319,6 +319,34 @@ def fetorax_config(width, heads, kv_heads, dim, ff, groups: int = 1) -> dict:
             "logit_softcap": 30.0, "max_positions": 8192}
 
 
+ZOPORAX_SIZES = {   # width, heads, unrotated / rotated / value size of a head, query and latent ranks, dense ff, experts, top, expert ff, shared ff
+    "1b": (2048, 16, 128, 64, 128, 768, 512, 8192, 64, 6, 1408, 2816),
+    "8b": (4096, 32, 128, 64, 128, 1536, 512, 14336, 64, 6, 2048, 4096),
+}
+
+
+def zoporax_config(size: str, window: int, groups: int = 1) -> dict:
+    """`groups` times four layers: latent attention and lightning by turns, a dense feed-forward behind the first
+    and routed experts (eight groups of which three are kept, a shared expert) behind the others."""
+    width, heads, dn, dr, dv, rq, rkv, ff, experts, top, eff, sff = ZOPORAX_SIZES[size]
+    lat = {"heads": heads, "dim": dn, "rot_dim": dr, "vdim": dv, "q_rank": rq, "kv_rank": rkv, "scale": (dn + dr) ** -0.5,
+           "mask": {"size": window},
+           "rot": {"dims": dr, "base": 1e4, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    lk = DESIGN_SIZES[size][3]
+    lig = {"heads": DESIGN_SIZES[size][1], "dim": lk, "vdim": lk,
+           "decay": [1.0 - 2.0 ** (-5 - 3 * h / DESIGN_SIZES[size][1]) for h in range(DESIGN_SIZES[size][1])]}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": sff},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 8, "keep": 3}}}
+    layers = []
+    for _ in range(groups):
+        layers += [{"type": "latent_attention", "mixer": dict(lat), "mlp": {"kind": "dense", "ff": ff}},
+                   {"type": "lightning", "mixer": dict(lig), "mlp": moe},
+                   {"type": "latent_attention", "mixer": dict(lat), "mlp": moe},
+                   {"type": "lightning", "mixer": dict(lig), "mlp": moe}]
+    return {"architecture": "Zoporax", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "layers": layers,
+            "max_positions": 8192}
+
+
 def _kernel_times(torch, run, warm: int = 2) -> tuple[dict, float]:
     """What every kind of kernel adds to the device time of one call of run(): {kind: (launches, total us)}, and the span."""
     import re
@@ -348,6 +376,138 @@ def _kernel_times(torch, run, warm: int = 2) -> tuple[dict, float]:
 
 
 def design_bench(args) -> int:
+    if args.design == "zoporax":
+        return zoporax_bench(args)
+    return fetorax_bench(args)
+
+
+def _design_run(torch, np, Engine, cfg, name, T, B, ctx, K, W, rng) -> dict:
+    """One model's prompt step and decode step: ms, tokens a second, and what every kind of kernel adds to each."""
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=B * (ctx + 256) + T + 64, max_batch=B + 1,
+                             max_context=ctx + 256, gain_std=0.0 if name == "llama" else 0.1)
+    prompt = rng.integers(0, DESIGN_VOCAB, T).tolist()
+
+    def prefill():
+        s = eng.new_sequence()
+        eng.step([(s, prompt)])
+        eng.end_sequence(s)
+    for _ in range(W):
+        prefill()
+    a, b = events(torch)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(max(3, K // 4)):
+        prefill()
+    b.record()
+    torch.cuda.synchronize()
+    prefill_ms = a.elapsed_time(b) / max(3, K // 4)
+    prefill_kinds, _ = _kernel_times(torch, prefill)
+    slots = [eng.new_sequence() for _ in range(B)]
+    eng.step([(s, rng.integers(0, DESIGN_VOCAB, ctx).tolist()) for s in slots])
+    feed = rng.integers(0, DESIGN_VOCAB, (W + K + 8, B))
+    at = [0]
+
+    def decode():
+        eng.step([(s, [int(t)]) for s, t in zip(slots, feed[at[0]])])
+        at[0] += 1
+    for _ in range(W):
+        decode()
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(K):
+        decode()
+    b.record()
+    torch.cuda.synchronize()
+    decode_ms = a.elapsed_time(b) / K
+    decode_kinds, _ = _kernel_times(torch, decode)
+    res = {"prefill_tokens_per_s": round(T / prefill_ms * 1e3), "prefill_ms": round(prefill_ms, 3),
+           "decode_tokens_per_s": round(B / decode_ms * 1e3), "decode_ms_per_step": round(decode_ms, 4),
+           "prefill_kernels_us": prefill_kinds, "decode_kernels_us": decode_kinds, "weight_bytes": eng.model.weight_bytes()}
+    eng.close()
+    del eng
+    torch.cuda.empty_cache()
+    return res
+
+
+def zoporax_bench(args) -> int:
+    """Prefill and decode of a Zoporax model of realistic layer sizes beside the closest model the library has, a
+    Fetorax model of attention and retention layers of the same width, depth and dense feed-forward (random weights,
+    vocabulary 32,000): tokens a second, what every kind of kernel adds to a prompt step and to a decode step, and
+    for the kernels that the design added how many times their roofline they take, beside the like kernel of
+    the other model (attention for latent attention; the scan is the same kernel in both)."""
+    import numpy as np
+    import torch
+
+    from longbow_quarrel_b200.engine import Engine
+    peaks, peaks_from = load_peaks()
+    K, W = args.steps, max(3, args.warmup)
+    T, B, ctx = PREFILL_TOKENS, BATCH, 2048
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size in args.sizes.split(","):
+        width, heads, kv, dim, ff = DESIGN_SIZES[size]
+        _, zh, dn, dr, dv, rq, rkv, _, experts, top, eff, sff = ZOPORAX_SIZES[size]
+        beside = fetorax_config(width, heads, kv, dim, ff)
+        for i, layer in enumerate(beside["layers"]):       # attention and retention by turns, each with keys of its own
+            if i % 2:
+                layer["type"], layer["mixer"] = "retention", dict(beside["layers"][1]["mixer"])
+            else:
+                layer["type"], layer["mixer"] = "attention", {k: v for k, v in beside["layers"][0]["mixer"].items() if k != "kv_from"}
+        configs = {"zoporax": zoporax_config(size, ctx + 256), "fetorax": beside}
+        res = {name: _design_run(torch, np, Engine, cfg, name, T, B, ctx, K, W, rng) for name, cfg in configs.items()}
+
+        def per_launch(kinds, *names):
+            n = sum(kinds[k][0] for k in names if k in kinds)
+            return sum(kinds[k][1] for k in names if k in kinds) / n if n else None
+
+        def times(us, nbytes, flops):
+            return round(us / (max(nbytes / hbm, flops / tensor) * 1e6), 2) if us else None
+        z, f = res["zoporax"], res["fetorax"]
+        Dk = rkv + dr
+        pairs = T * (T + 1) / 2
+        roof = {
+            "prefill": {
+                "fetorax attention": times(per_launch(f["prefill_kernels_us"], "attn_prefill_two", "attn_prefill_tc", "attn_prefill"),
+                                           T * heads * 3 * dim * 2.0, 4.0 * heads * dim * pairs),
+                "zoporax latent attention": times(per_launch(z["prefill_kernels_us"], "latent_attention", "latent_attention_tc"),
+                                                  T * zh * (Dk + rkv) * 4.0 + T * Dk * 2.0, 2.0 * zh * (Dk + rkv) * pairs),
+                "zoporax per-head matrices": times(per_launch(z["prefill_kernels_us"], "head_matmul", "head_matmul_tc"),
+                                                   T * zh * (dn + rkv + dv) * 3.0, 2.0 * T * zh * rkv * (dn + dv) / 2),
+                "fetorax recurrent scan": times(per_launch(f["prefill_kernels_us"], "linear_scan"),
+                                                T * heads * 3 * dim * 2.0 + T * heads * dim * 4.0, 4.0 * T * heads * dim * dim),
+                "zoporax recurrent scan": times(per_launch(z["prefill_kernels_us"], "linear_scan"),
+                                                T * heads * 3 * dim * 2.0 + T * heads * dim * 4.0, 4.0 * T * heads * dim * dim),
+                "zoporax experts, first product": times(per_launch(z["prefill_kernels_us"], "moe_up", "moe_up_tc"),
+                                                        experts * eff * width * 2.0, 2.0 * T * top * eff * width),
+                "zoporax experts, second product": times(per_launch(z["prefill_kernels_us"], "moe_down", "moe_down_tc"),
+                                                         experts * eff * width * 2.0, 2.0 * T * top * eff * width),
+            },
+            "decode": {
+                "fetorax attention": times(per_launch(f["decode_kernels_us"], "attn_decode"), B * ctx * 2 * kv * dim * 2.0, 0.0),
+                "zoporax latent attention": times(per_launch(z["decode_kernels_us"], "latent_attention", "latent_attention_tc"),
+                                                  B * ctx * Dk * 2.0, 0.0),
+                "fetorax recurrent scan": times(per_launch(f["decode_kernels_us"], "linear_scan_single"), B * heads * dim * dim * 8.0, 0.0),
+                "zoporax recurrent scan": times(per_launch(z["decode_kernels_us"], "linear_scan_single"), B * heads * dim * dim * 8.0, 0.0),
+                "zoporax experts, first product": times(per_launch(z["decode_kernels_us"], "moe_up"), min(B * top, experts) * eff * width * 2.0, 0.0),
+                "zoporax experts, second product": times(per_launch(z["decode_kernels_us"], "moe_down"), min(B * top, experts) * eff * width * 2.0, 0.0),
+            },
+        }
+        out[size] = {"zoporax": z, "fetorax": f, "times_the_roofline": roof,
+                     "zoporax_over_fetorax": {"prefill": round(z["prefill_tokens_per_s"] / f["prefill_tokens_per_s"], 3),
+                                              "decode": round(z["decode_tokens_per_s"] / f["decode_tokens_per_s"], 3)}}
+    clocks = sampler.stop()
+    print(json.dumps({"design": "zoporax", "beside": "fetorax", "dtype": "bf16", "data": "synthetic", "layers": 4,
+                      "layer_order": "latent attention + dense, lightning + experts, latent attention + experts, lightning + experts; "
+                                     "beside attention, retention, attention, retention, each + dense",
+                      "vocab": DESIGN_VOCAB, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx, "steps": K,
+                      "warmup": W, "peaks": peaks, "peaks_from": peaks_from, "clocks": clocks, "sizes": out}))
+    return 0
+
+
+def fetorax_bench(args) -> int:
     """Prefill and decode of a Fetorax model of the 1B and 8B layer sizes beside a Llama model of the same sizes
     (random weights, vocabulary cut to 32,000): tokens a second, the device time of every kind of kernel in one
     prompt step and one decode step, and for the kernels that the design added how many times their roofline
@@ -456,8 +616,9 @@ def design_bench(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default="", choices=["", "fetorax"],
-                    help="instead of the default workload: this design beside Llama at equal layer sizes (prefill, decode, kernel by kernel)")
+    ap.add_argument("--design", default="", choices=["", "fetorax", "zoporax"],
+                    help="instead of the default workload: this design beside the closest model the library has, at equal layer "
+                         "sizes (prefill, decode, kernel by kernel): fetorax beside Llama, zoporax beside Fetorax")
     ap.add_argument("--sizes", default="1b,8b", help="--design: layer sizes to run, of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
