@@ -478,6 +478,42 @@ def latent_attention(q: torch.Tensor, pages: torch.Tensor, page_table, tok_pos, 
     return out
 
 
+def latent_tc_tokens(H: int) -> int:
+    """Tokens of one block of latent_attention_tc for H heads: as many as fit, with all their heads, into its 64 rows."""
+    return 1 if H >= 64 else 64 // H
+
+
+def latent_attention_tc_takes(pages: torch.Tensor, page_size: int) -> bool:
+    """Whether the tensor-core kernel serves this cache: bfloat16 rows of a multiple of 8 numbers, pages of a multiple of 32."""
+    return pages.dtype == torch.bfloat16 and pages.shape[-1] % 8 == 0 and page_size % 32 == 0
+
+
+def latent_attention_tc(q: torch.Tensor, pages: torch.Tensor, page_table, slots, H: int, R: int, page_size: int, scale: float,
+                        window: int | None, blocks: tuple | None = None, tok_pos=None, tok_seq=None, splits: int = 1) -> torch.Tensor:
+    """latent_attention on the tensor cores (mma.sync, bfloat16 cache rows).  blocks = (sequence, first row, tokens, first
+    position) int32 tensors, one entry per block of at most latent_tc_tokens(H) consecutive tokens of one sequence, for
+    a step with prompts; without it every row is its own block (tok_pos, tok_seq) and its keys may be cut into `splits`."""
+    T, Hq, Dk = q.shape
+    if q.dtype != torch.float32 or not q.is_contiguous() or Hq != H or pages.shape[-1] != Dk or not pages.is_contiguous():
+        raise KernelError("latent_attention_tc: contiguous float32 queries [T, H, Dk] and cache rows of Dk numbers")
+    if not latent_attention_tc_takes(pages, page_size):
+        raise KernelError("latent_attention_tc takes bfloat16 cache rows of a multiple of 8 numbers in pages of a multiple of 32")
+    out = torch.empty((T, H, R), dtype=torch.float32, device=q.device)
+    part_o = part_ml = None
+    if blocks is not None:
+        splits = 1
+    if splits > 1:
+        part_o = torch.empty((T, H, splits, R), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T, H, splits, 2), dtype=torch.float32, device=q.device)
+    qb = blocks if blocks is not None else (None, None, None, None)
+    fn = _fn("latent_attn_tc", "lq_latent_attention_tc", [c_void_p] * 14 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p])
+    _check(fn(_p(q), _p(pages), _p(page_table), page_table.stride(0), _p(slots), _p(qb[0]), _p(qb[1]), _p(qb[2]), _p(qb[3]),
+              _p(tok_pos), _p(tok_seq), _p(out), _p(part_o), _p(part_ml), qb[0].numel() if blocks is not None else T, T, H, R, Dk,
+              page_size, float(scale), int(window or 0), int(splits), _stream()),
+           "latent_attention_tc", 2 if splits > 1 else 1, "latent_attention_tc:slices" if splits > 1 else None)
+    return out
+
+
 # ------------------------------------------------------------------ routed feed-forward
 MOE_ACTS = {None: 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
 

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import attention as attention_kernels
 from ..kernels import linear, ops
 from ..weights.spec import WeightSpec
 from .base import KVNeed, Mixer, Runtime, StepContext
@@ -36,7 +37,10 @@ MIN_KEYS_PER_SLICE = 128      # single tokens: a slice of a row's keys shorter t
 class LatentAttention(Mixer):
     graph_safe = True
     returns_branch = True
-    kernel_libraries = ("latent_attn",)
+
+    @property
+    def kernel_libraries(self):
+        return ("latent_attn", "latent_attn_tc") if self.runtime.dtype == torch.bfloat16 else ("latent_attn",)
 
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, head_dim: int, rot_dim: int, value_dim: int,
                  q_rank: int, kv_rank: int, scale: float, eps: float, position: PartSpec | None = None,
@@ -59,6 +63,13 @@ class LatentAttention(Mixer):
 
     def cache_need(self):
         return KVNeed(1, self.R + self.dr, self.window, values=False)
+
+    def step_needs(self):
+        """The tensor-core kernel's work list for steps with prompts: blocks of consecutive tokens of one sequence."""
+        if self.runtime.dtype != torch.bfloat16 or (self.R + self.dr) % 8:
+            return {}
+        size = ops.latent_tc_tokens(self.H)
+        return {f"latent_blocks{size}": attention_kernels.query_blocks(size)}
 
     def weights(self):
         n, H = self.names, self.H
@@ -88,14 +99,30 @@ class LatentAttention(Mixer):
         self.w_uk = tensors[n["uk"]].reshape(H, self.dn, self.R).contiguous()
         self.w_uv = tensors[n["uv"]].reshape(H, self.dv, self.R).transpose(1, 2).contiguous()
 
-    def _splits(self, ctx: StepContext) -> int:
+    def _splits(self, ctx: StepContext, blocks_per_token: int, places_per_sm: int = 1) -> int:
         """Slices per row for a step of single tokens: as many as fill the multiprocessors, none shorter than
         MIN_KEYS_PER_SLICE.  A fixed number per batch size (the step may be captured and replayed)."""
         if not ctx.decode:
             return 1
         reach = min(self.window or self.runtime.max_context, self.runtime.max_context)
-        blocks = ctx.T * -(-self.H // 8)
-        return max(1, min(ops.sm_count(self.runtime.device) // max(blocks, 1), reach // MIN_KEYS_PER_SLICE, 32))
+        blocks = max(ctx.T * blocks_per_token, 1)
+        return max(1, min(places_per_sm * ops.sm_count(self.runtime.device) // blocks, reach // MIN_KEYS_PER_SLICE, 32))
+
+    def _attend(self, wide, pages, ctx: StepContext, cache_view):
+        """The weighted means of latent rows, float32 [T, H, R]: on the tensor cores where the cache allows it."""
+        H, R = self.H, self.R
+        if ops.latent_attention_tc_takes(pages, cache_view.page_size):
+            chunks = -(-R // (64 if R <= 64 else 128 if R <= 128 else 256))
+            if ctx.decode:
+                return ops.latent_attention_tc(wide, pages, cache_view.page_table, ctx.slots, H, R, cache_view.page_size,
+                                               self.scale, self.window, tok_pos=ctx.tok_pos, tok_seq=ctx.tok_seq,
+                                               splits=self._splits(ctx, -(-H // 64) * chunks, 2))
+            flat = ctx.extra.get(f"latent_blocks{ops.latent_tc_tokens(H)}")
+            if flat is not None and flat.numel():
+                return ops.latent_attention_tc(wide, pages, cache_view.page_table, ctx.slots, H, R, cache_view.page_size,
+                                               self.scale, self.window, blocks=tuple(flat.view(4, -1)))
+        return ops.latent_attention(wide, pages, cache_view.page_table, ctx.tok_pos, ctx.tok_seq, ctx.slots, H, R,
+                                    cache_view.page_size, self.scale, self.window, self._splits(ctx, -(-H // 8)))
 
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
         if not writes_cache:
@@ -114,8 +141,7 @@ class LatentAttention(Mixer):
         wide2 = wide.view(T, H * (R + dr))
         ops.head_matmul(q, dn + dr, 0, self.w_uk, wide2, R + dr, 0)              # W_uk,h^T q_h
         ops.rope_tail(q, dn + dr, dn, wide2, R + dr, R, cos, sin, self.rot, ctx.tok_pos, H, dr)
-        mean = ops.latent_attention(wide, pages, cache_view.page_table, ctx.tok_pos, ctx.tok_seq, ctx.slots, H, R,
-                                    cache_view.page_size, self.scale, self.window, self._splits(ctx))
+        mean = self._attend(wide, pages, ctx, cache_view)
         out = torch.empty((T, H * dv), dtype=act, device=q.device)
         ops.head_matmul(mean.view(T, H * R), R, 0, self.w_uv, out, dv, 0)        # W_uv,h (sum_j p_j c_j)
         if self.gate is not None:

@@ -318,3 +318,82 @@ def test_the_scan_with_silu_on_its_inputs_in_pieces_and_single_tokens(dtype, H, 
             at += m
         assert _rel(torch.cat(got), ref) < 1e-5, pieces[:3]
         assert _rel(state[1], S) < 1e-5 and float(state[0].abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------ the attention on the tensor cores
+
+def _blocks_for(new, past, size):
+    """The work list of a step whose sequences bring `new` tokens after `past`: the framework's own builder."""
+    from longbow_quarrel_b200.kernels.attention import query_blocks
+    from longbow_quarrel_b200.parts.base import StepShape
+    cu = np.concatenate([[0], np.cumsum(new)])
+    flat = query_blocks(size)(StepShape(B=len(new), T=int(sum(new)), past=tuple(past), new=tuple(new), cu=tuple(int(c) for c in cu)))
+    return tuple(_i32(row.tolist()) for row in flat)
+
+
+@pytest.mark.parametrize("H,R,dr,window", [(3, 24, 8, 33), (1, 20, 12, None), (8, 96, 24, 64), (9, 40, 16, 100), (16, 300, 20, 70),
+                                           (70, 16, 8, 64), (4, 512, 64, 150)])
+def test_tensor_core_attention_over_latent_rows_prompts_portions_and_single_tokens(H, R, dr, window):
+    """Three sequences in one launch: a whole prompt from its first token, a portion that goes on after 83 cached tokens
+    (across page borders and the window's edge), a short prompt; then single tokens with their keys cut into slices.
+    Against a float64 restatement that reads the same rounded queries and cache rows."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(H * 100 + R)
+    Dk, page_size = R + dr, 64
+    lens = {0: 200, 2: 70, 3: 17}
+    rows = {s: torch.randn(n, Dk, generator=g) for s, n in lens.items()}
+    pages, table = _paged(rows, Dk, page_size, torch.bfloat16, 9, seed=H)
+    stored = {s: r.to(torch.bfloat16).double() for s, r in rows.items()}
+    slots = [2, 0, 3]
+    w = window or 0
+    new, past = [70, 117, 17], [0, 83, 0]
+    pos = [p for n, b in zip(new, past) for p in range(b, b + n)]
+    seq = [i for i, n in enumerate(new) for _ in range(n)]
+    T = len(pos)
+    q = torch.randn(T, H, Dk, generator=g)
+    qr = q.to(torch.bfloat16).double()
+    out = ops.latent_attention_tc(q.to(DEV), pages, table, _i32(slots), H, R, page_size, 0.2, window,
+                                  blocks=_blocks_for(new, past, ops.latent_tc_tokens(H)))
+    for t in range(T):
+        ref = _latent_reference(qr[t], stored[slots[seq[t]]], pos[t], w, R, 0.2)
+        assert _rel(out[t], ref) < 6e-3, (t, pos[t], seq[t])
+    # single tokens: the last row of each sequence, and one in the middle of the long one
+    for splits in (1, 3):
+        pos1, seq1 = [199, 69, 16], [1, 0, 2]
+        q1 = torch.randn(3, H, Dk, generator=g)
+        out = ops.latent_attention_tc(q1.to(DEV), pages, table, _i32(slots), H, R, page_size, 0.2, window, tok_pos=_i32(pos1),
+                                      tok_seq=_i32(seq1), splits=splits)
+        for t in range(3):
+            ref = _latent_reference(q1[t].to(torch.bfloat16).double(), stored[slots[seq1[t]]], pos1[t], w, R, 0.2)
+            assert _rel(out[t], ref) < 6e-3, (splits, t)
+
+
+@pytest.mark.parametrize("window", [40, 64, 257])
+@pytest.mark.parametrize("splits", [1, 5])
+def test_tensor_core_attention_finds_the_key_that_outweighs_all_others_up_to_the_window_edge(window, splits):
+    ops = _ops()
+    g = torch.Generator().manual_seed(window)
+    H, R, dr, page_size = 2, 32, 8, 64
+    Dk, n, planted = R + dr, 700, 300
+    rows = 0.1 * torch.randn(n, Dk, generator=g)
+    direction = torch.randn(Dk, generator=g)
+    direction /= direction.norm()
+    rows[planted] = 8.0 * direction
+    pages, table = _paged({1: rows}, Dk, page_size, torch.bfloat16, 12, seed=window)
+    stored = rows.to(torch.bfloat16).double()
+    # as a portion of a prompt: positions planted .. planted + window + 1 in one step; as single tokens: the edge itself
+    first, count = planted, window + 2
+    q = (8.0 * direction).repeat(count, H, 1)
+    for win in (window, None):
+        out = ops.latent_attention_tc(q.to(DEV), pages, table, _i32([1]), H, R, page_size, 1.0, win,
+                                      blocks=_blocks_for([count], [first], ops.latent_tc_tokens(H)))
+        edge = [(window - 1, True), (window, win is None), (window + 1, win is None), (0, True), (1, True)]
+        for off, sees in edge:
+            closeness = _rel(out[off, 0], stored[planted, :R])
+            assert (closeness < 1e-2) == sees, (win, off, closeness)
+        pos1 = [planted + window - 1, planted + window, n - 1]
+        out = ops.latent_attention_tc(q[:3].to(DEV), pages, table, _i32([1]), H, R, page_size, 1.0, win, tok_pos=_i32(pos1),
+                                      tok_seq=_i32([0, 0, 0]), splits=splits)
+        for t, sees in enumerate([True, win is None, win is None]):
+            closeness = _rel(out[t, 0], stored[planted, :R])
+            assert (closeness < 1e-2) == sees, (win, pos1[t], closeness)
