@@ -1,0 +1,242 @@
+// Many small matrix products in one launch, on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums):
+//
+//     out[row(r), g-th column block] = epilogue( A[a_row(r), g-th column block] . W[g]^T )      W[g] [N, K], K contiguous
+//
+// for groups g = 0 .. G-1.  Two ways of saying which rows belong to a group:
+//   uniform   every group has the same M rows 0 .. M-1 (one small matrix per head: a_group_stride / o_group_stride
+//             move A and out from head to head inside a row)
+//   listed    `rows` lists row numbers group by group, group g owning rows[group_off[g] .. group_off[g+1]) (routed
+//             experts: the (token, choice) pairs sorted by expert; A's row is rows[r] / a_div, so that the `top`
+//             choices of a token read the token's one input row; out's row is rows[r]).  lq_group_rows makes the list
+//             on the device from the chosen experts, so that nothing of a step waits for the host.
+// A block makes a 64 x 128 tile of one group: 2 x 2 warps of 32 x 64, operands through shared memory in steps of
+// 32 along K (cp.async, two stages, rows padded against bank conflicts).
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int BM = 64, BN = 128, BK = 32, PAD = 8, NT = 128, LDS = BK + PAD;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// act: 0 none, 1 gelu (erf), 2 gelu (tanh form), 3 silu, 4 relu
+__device__ __forceinline__ float gg_act(float v, int act) {
+    switch (act) {
+        case 1: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+        case 2: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        case 3: return v / (1.f + expf(-v));
+        case 4: return fmaxf(v, 0.f);
+        default: return v;
+    }
+}
+
+struct GroupedArgs {
+    const __nv_bfloat16* A;
+    long long lda, a_group_stride;
+    int a_div;
+    const __nv_bfloat16* W;
+    long long w_group_stride;
+    void* out;
+    long long ldo, o_group_stride;
+    const int* rows;                 // listed: row numbers, group by group (null: uniform)
+    const int* group_off;            // listed: [G + 1]
+    const int* tile_off;             // listed: [G + 1] prefix of each group's row tiles
+    int G, M, N, K, act;
+};
+
+template <typename TO>
+__global__ void __launch_bounds__(NT) grouped_gemm_kernel(GroupedArgs a) {
+    __shared__ __align__(16) __nv_bfloat16 sa[2][BM][LDS];
+    __shared__ __align__(16) __nv_bfloat16 sb[2][BN][LDS];
+    __shared__ int s_rows[BM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
+    const int wm = warp >> 1, wn = warp & 1;
+    pdl_launch_dependents();
+    pdl_wait();
+    // Which group, and which of its row tiles.
+    int g, r_first, r_end;
+    if (a.rows) {
+        const int tile = blockIdx.x;
+        if (tile >= a.tile_off[a.G]) return;
+        int lo = 0, hi = a.G - 1;
+        while (lo < hi) {                        // the last group whose first tile is not beyond this one
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.tile_off[mid] <= tile) lo = mid; else hi = mid - 1;
+        }
+        g = lo;
+        r_first = a.group_off[g] + (tile - a.tile_off[g]) * BM;
+        r_end = a.group_off[g + 1];
+    } else {
+        const int tiles = (a.M + BM - 1) / BM;
+        g = blockIdx.x / tiles;
+        r_first = (blockIdx.x % tiles) * BM;
+        r_end = a.M;
+    }
+    const int n_rows = min(BM, r_end - r_first), n0 = blockIdx.y * BN;
+    if (tid < BM) s_rows[tid] = tid < n_rows ? (a.rows ? a.rows[r_first + tid] : r_first + tid) : -1;
+    __syncthreads();
+    const __nv_bfloat16* A = a.A + (long long)g * a.a_group_stride;
+    const __nv_bfloat16* W = a.W + (long long)g * a.w_group_stride;
+    const int K = a.K, N = a.N;
+    auto load = [&](int k0, int stage) {
+        for (int i = tid; i < BM * (BK / 8); i += NT) {
+            const int r = i / (BK / 8), c = k0 + (i % (BK / 8)) * 8, row = s_rows[r];
+            const bool ok = row >= 0 && c < K;
+            cp_async16((uint32_t)__cvta_generic_to_shared(&sa[stage][r][c - k0]), ok ? A + (long long)(row / a.a_div) * a.lda + c : A, ok);
+        }
+        for (int i = tid; i < BN * (BK / 8); i += NT) {
+            const int r = i / (BK / 8), c = k0 + (i % (BK / 8)) * 8;
+            const bool ok = n0 + r < N && c < K;
+            cp_async16((uint32_t)__cvta_generic_to_shared(&sb[stage][r][c - k0]), ok ? W + (long long)(n0 + r) * K + c : W, ok);
+        }
+    };
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+    const int steps = (K + BK - 1) / BK;
+    load(0, 0);
+    cp_async_commit();
+    for (int s = 0; s < steps; ++s) {
+        const int stage = s & 1;
+        if (s + 1 < steps) load((s + 1) * BK, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = kk * 16 + (lane >> 4) * 8;
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(&sa[stage][r][c]), af[i][0], af[i][1], af[i][2], af[i][3]);
+            }
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                const int r = wn * 64 + jp * 16 + (lane & 7) + (lane >> 4) * 8, c = kk * 16 + ((lane >> 3) & 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(&sb[stage][r][c]), b0, b1, b2, b3);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_bf16(acc[i][2 * jp], af[i][0], af[i][1], af[i][2], af[i][3], b0, b1);
+                    mma_bf16(acc[i][2 * jp + 1], af[i][0], af[i][1], af[i][2], af[i][3], b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    TO* out = (TO*)a.out + (long long)g * a.o_group_stride;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = s_rows[wm * 32 + i * 16 + gq + half * 8];
+            if (row < 0) continue;
+            TO* o = out + (long long)row * a.ldo;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int n = n0 + wn * 64 + j * 8 + 2 * t;
+                if (n < N) o[n] = from_f32<TO>(gg_act(acc[i][j][2 * half], a.act));
+                if (n + 1 < N) o[n + 1] = from_f32<TO>(gg_act(acc[i][j][2 * half + 1], a.act));
+            }
+        }
+}
+
+// ids [n] (each in [0, G)) -> rows [n]: the indices 0 .. n-1 group by group; group_off [G + 1]; tile_off [G + 1]: the
+// prefix of ceil(count / 64).  One block; the order inside a group is whatever the atomics give (no result depends on it).
+__global__ void __launch_bounds__(1024) group_rows_kernel(const int* __restrict__ ids, int n, int G, int* __restrict__ rows,
+                                                          int* __restrict__ group_off, int* __restrict__ tile_off) {
+    pdl_launch_dependents();
+    extern __shared__ int sm[];                  // [G] counts, then [G] cursors
+    int* count = sm;
+    int* cursor = sm + G;
+    pdl_wait();
+    for (int g = threadIdx.x; g < G; g += blockDim.x) count[g] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int g = 0; g < G; ++g) {
+            group_off[g] = at;
+            tile_off[g] = tiles;
+            cursor[g] = at;
+            at += count[g];
+            tiles += (count[g] + BM - 1) / BM;
+        }
+        group_off[G] = at;
+        tile_off[G] = tiles;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) rows[atomicAdd(&cursor[ids[i]], 1)] = i;
+}
+
+// x[t, :] (+)= sum_j weights[t, j] y[t * top + j, :] (+ sigmoid(zs[t]) * shared[t, :]), the choices added in their order.
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
+                                                          const float* __restrict__ shared, const float* __restrict__ zs,
+                                                          int zs_stride, float* __restrict__ x, int accumulate, int top, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
+    for (int d = threadIdx.x; d < D; d += 256) {
+        float s = 0.f;
+        for (int j = 0; j < top; ++j) s = fmaf(weights[(size_t)t * top + j], y[((size_t)t * top + j) * D + d], s);
+        if (shared) s = fmaf(sg, shared[(size_t)t * D + d], s);
+        float* o = x + (size_t)t * D + d;
+        *o = accumulate ? *o + s : s;
+    }
+}
+
+}  // namespace
+
+LQ_EXPORT int lq_group_rows(const int* ids, int n, int G, int* rows, int* group_off, int* tile_off, cudaStream_t stream) {
+    if (n <= 0 || G <= 0) return LQ_BAD_SIZE;
+    const size_t smem = 2 * (size_t)G * sizeof(int);
+    if (smem > 48 * 1024) return LQ_BAD_SIZE;
+    return launch_pdl(group_rows_kernel, dim3(1), dim3(1024), smem, stream, ids, n, G, rows, group_off, tile_off);
+}
+
+// Row tiles that a listed launch of n rows in G groups can need at most.
+LQ_EXPORT int lq_grouped_gemm_tiles(int n, int G) { return (n + BM - 1) / BM + G; }
+
+LQ_EXPORT int lq_grouped_gemm(const void* A, long long lda, long long a_group_stride, int a_div, const void* W,
+                              long long w_group_stride, void* out, int out_dtype, long long ldo, long long o_group_stride,
+                              const int* rows, const int* group_off, const int* tile_off, int n_listed, int G, int M, int N,
+                              int K, int act, cudaStream_t stream) {
+    if (G <= 0 || N <= 0) return LQ_OK;
+    if (K % 8 || lda % 8 || a_group_stride % 8 || w_group_stride % 8 || a_div < 1 || act < 0 || act > 4) return LQ_BAD_SIZE;
+    if (((uintptr_t)A | (uintptr_t)W) & 15) return LQ_BAD_SIZE;
+    if (rows ? (!group_off || !tile_off || n_listed <= 0) : M <= 0) return LQ_BAD_SIZE;
+    GroupedArgs a{(const __nv_bfloat16*)A, lda, a_group_stride, a_div, (const __nv_bfloat16*)W, w_group_stride, out, ldo,
+                  o_group_stride, rows, group_off, tile_off, G, M, N, K, act};
+    dim3 grid(rows ? lq_grouped_gemm_tiles(n_listed, G) : G * ((M + BM - 1) / BM), (N + BN - 1) / BN);
+    if (out_dtype == LQ_F32) return launch_pdl(grouped_gemm_kernel<float>, grid, dim3(NT), 0, stream, a);
+    if (out_dtype == LQ_BF16) return launch_pdl(grouped_gemm_kernel<__nv_bfloat16>, grid, dim3(NT), 0, stream, a);
+    return LQ_BAD_DTYPE;
+}
+
+LQ_EXPORT int lq_moe_combine(const float* y, const float* weights, const float* shared, const float* zs, int zs_stride, float* x,
+                             int accumulate, int T, int top, int D, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    return launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, weights, shared, zs, zs_stride, x, accumulate, top, D);
+}

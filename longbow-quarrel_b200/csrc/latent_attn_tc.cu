@@ -60,10 +60,11 @@ struct LatentArgs {
     const int* qb_pos;
     const int* tok_pos;              // steps of single tokens
     const int* tok_seq;
-    float* out;                      // [T, H, R]
+    float* out;                      // [T, H, R] (bfloat16 with out_bf16)
     float* part_o;                   // [T, H, splits, R]
     float* part_ml;                  // [T, H, splits, 2]: maximum (natural logarithm units) and sum
     int H, R, Dk, page_size, window, splits, head_blocks, chunks;
+    int out_bf16;                    // the final rows go out as bfloat16 (the partial results of slices stay float32)
     float scale_log2;
 };
 
@@ -223,13 +224,23 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
         const int r = half ? r1 : r0;
         if (!(half ? row1ok : row0ok)) continue;
         const size_t pair = (size_t)(row0 + r / Hb) * H + h0 + r % Hb;
-        float* dst = whole ? a.out + pair * R : a.part_o + (pair * a.splits + split) * R;
         const float inv = half ? i1 : i0;
+        if (whole && a.out_bf16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.out) + pair * R;
 #pragma unroll
-        for (int j = 0; j < CW / 8; ++j) {
-            const int d = c0 + j * 8 + 2 * t;
-            if (d < R) dst[d] = o[j][2 * half] * inv;
-            if (d + 1 < R) dst[d + 1] = o[j][2 * half + 1] * inv;
+            for (int j = 0; j < CW / 8; ++j) {
+                const int d = c0 + j * 8 + 2 * t;
+                if (d < R) dst[d] = __float2bfloat16_rn(o[j][2 * half] * inv);
+                if (d + 1 < R) dst[d + 1] = __float2bfloat16_rn(o[j][2 * half + 1] * inv);
+            }
+        } else {
+            float* dst = whole ? a.out + pair * R : a.part_o + (pair * a.splits + split) * R;
+#pragma unroll
+            for (int j = 0; j < CW / 8; ++j) {
+                const int d = c0 + j * 8 + 2 * t;
+                if (d < R) dst[d] = o[j][2 * half] * inv;
+                if (d + 1 < R) dst[d + 1] = o[j][2 * half + 1] * inv;
+            }
         }
         if (!whole && chunk == 0 && t == 0) {
             float* ml = a.part_ml + (pair * a.splits + split) * 2;
@@ -240,8 +251,9 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
 }
 
 // One warp per (row, head): the slices' results combined in the order of the slices.
+template <typename TO>
 __global__ void __launch_bounds__(128) latent_merge_tc_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                              float* __restrict__ out, int n_pairs, int R, int splits) {
+                                                              TO* __restrict__ out, int n_pairs, int R, int splits) {
     pdl_launch_dependents();
     pdl_wait();
     const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -256,7 +268,7 @@ __global__ void __launch_bounds__(128) latent_merge_tc_kernel(const float* __res
         float o = 0.f;
         for (int s = 0; s < splits; ++s)
             if (ml[2 * s] != -CUDART_INF_F) o = fmaf(part_o[((size_t)pair * splits + s) * R + d], expf(ml[2 * s] - m), o);
-        out[(size_t)pair * R + d] = o * inv;
+        out[(size_t)pair * R + d] = from_f32<TO>(o * inv);
     }
 }
 
@@ -273,7 +285,10 @@ int launch(LatentArgs a, int n_blocks, int T, cudaStream_t stream) {
     int rc = launch_pdl(latent_attention_tc_kernel<CW>, grid, dim3(NT), smem, stream, a);
     if (rc != LQ_OK || a.splits == 1) return rc;
     const int n = T * a.H;
-    return launch_pdl(latent_merge_tc_kernel, dim3((n + 3) / 4), dim3(128), 0, stream, (const float*)a.part_o,
+    if (a.out_bf16)
+        return launch_pdl(latent_merge_tc_kernel<__nv_bfloat16>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float*)a.part_o,
+                          (const float*)a.part_ml, reinterpret_cast<__nv_bfloat16*>(a.out), n, a.R, a.splits);
+    return launch_pdl(latent_merge_tc_kernel<float>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float*)a.part_o,
                       (const float*)a.part_ml, a.out, n, a.R, a.splits);
 }
 
@@ -287,14 +302,16 @@ LQ_EXPORT int lq_latent_attention_tc_tokens(int H) { return H >= BM ? 1 : BM / H
 // place).  Dk a multiple of 8, page_size a multiple of 32, bfloat16 cache rows.
 LQ_EXPORT int lq_latent_attention_tc(const float* q, const void* pages, const int* page_table, int pt_stride, const int* slots,
                                      const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos,
-                                     const int* tok_pos, const int* tok_seq, float* out, float* part_o, float* part_ml,
+                                     const int* tok_pos, const int* tok_seq, void* out, int out_dtype, float* part_o, float* part_ml,
                                      int n_blocks, int T, int H, int R, int Dk, int page_size, float scale, int window,
                                      int splits, cudaStream_t stream) {
     if (n_blocks <= 0) return LQ_OK;
     if (Dk % 8 || R < 1 || R > Dk || page_size % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return LQ_BAD_SIZE;
     if (!qb_seq && (!tok_pos || !tok_seq)) return LQ_BAD_SIZE;
+    if (out_dtype != LQ_F32 && out_dtype != LQ_BF16) return LQ_BAD_DTYPE;
     LatentArgs a{q, (const __nv_bfloat16*)pages, page_table, pt_stride, slots, qb_seq, qb_row, qb_rows, qb_pos, tok_pos, tok_seq,
-                 out, part_o, part_ml, H, R, Dk, page_size, window, splits, (H + BM - 1) / BM, 1, scale * 1.4426950408889634f};
+                 (float*)out, part_o, part_ml, H, R, Dk, page_size, window, splits, (H + BM - 1) / BM, 1, out_dtype == LQ_BF16,
+                 scale * 1.4426950408889634f};
     if (R <= 64) return launch<64>(a, n_blocks, T, stream);
     if (R <= 128) return launch<128>(a, n_blocks, T, stream);
     return launch<256>(a, n_blocks, T, stream);

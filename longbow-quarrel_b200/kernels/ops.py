@@ -489,16 +489,18 @@ def latent_attention_tc_takes(pages: torch.Tensor, page_size: int) -> bool:
 
 
 def latent_attention_tc(q: torch.Tensor, pages: torch.Tensor, page_table, slots, H: int, R: int, page_size: int, scale: float,
-                        window: int | None, blocks: tuple | None = None, tok_pos=None, tok_seq=None, splits: int = 1) -> torch.Tensor:
+                        window: int | None, blocks: tuple | None = None, tok_pos=None, tok_seq=None, splits: int = 1,
+                        out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """latent_attention on the tensor cores (mma.sync, bfloat16 cache rows).  blocks = (sequence, first row, tokens, first
     position) int32 tensors, one entry per block of at most latent_tc_tokens(H) consecutive tokens of one sequence, for
-    a step with prompts; without it every row is its own block (tok_pos, tok_seq) and its keys may be cut into `splits`."""
+    a step with prompts; without it every row is its own block (tok_pos, tok_seq) and its keys may be cut into `splits`.
+    Returns [T, H, R] in out_dtype (float32 or bfloat16)."""
     T, Hq, Dk = q.shape
     if q.dtype != torch.float32 or not q.is_contiguous() or Hq != H or pages.shape[-1] != Dk or not pages.is_contiguous():
         raise KernelError("latent_attention_tc: contiguous float32 queries [T, H, Dk] and cache rows of Dk numbers")
     if not latent_attention_tc_takes(pages, page_size):
         raise KernelError("latent_attention_tc takes bfloat16 cache rows of a multiple of 8 numbers in pages of a multiple of 32")
-    out = torch.empty((T, H, R), dtype=torch.float32, device=q.device)
+    out = torch.empty((T, H, R), dtype=out_dtype, device=q.device)
     part_o = part_ml = None
     if blocks is not None:
         splits = 1
@@ -506,12 +508,66 @@ def latent_attention_tc(q: torch.Tensor, pages: torch.Tensor, page_table, slots,
         part_o = torch.empty((T, H, splits, R), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T, H, splits, 2), dtype=torch.float32, device=q.device)
     qb = blocks if blocks is not None else (None, None, None, None)
-    fn = _fn("latent_attn_tc", "lq_latent_attention_tc", [c_void_p] * 14 + [c_int] * 6 + [c_float, c_int, c_int, c_void_p])
+    fn = _fn("latent_attn_tc", "lq_latent_attention_tc", [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 8 + [c_int, c_void_p, c_void_p]
+             + [c_int] * 6 + [c_float, c_int, c_int, c_void_p])
     _check(fn(_p(q), _p(pages), _p(page_table), page_table.stride(0), _p(slots), _p(qb[0]), _p(qb[1]), _p(qb[2]), _p(qb[3]),
-              _p(tok_pos), _p(tok_seq), _p(out), _p(part_o), _p(part_ml), qb[0].numel() if blocks is not None else T, T, H, R, Dk,
+              _p(tok_pos), _p(tok_seq), _p(out), dtype_code(out), _p(part_o), _p(part_ml), qb[0].numel() if blocks is not None else T, T, H, R, Dk,
               page_size, float(scale), int(window or 0), int(splits), _stream()),
            "latent_attention_tc", 2 if splits > 1 else 1, "latent_attention_tc:slices" if splits > 1 else None)
     return out
+
+
+# ------------------------------------------------------------------ many small products in one launch
+def grouped_gemm_takes(a: torch.Tensor, w: torch.Tensor, a_group_stride: int = 0) -> bool:
+    """Whether grouped_gemm serves these operands: bfloat16, rows and groups that start on 16-byte boundaries."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[-1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a_group_stride % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_group_stride: int = 0, o_group_stride: int = 0,
+                 listed: tuple | None = None, a_div: int = 1, act: str | None = None) -> torch.Tensor:
+    """out[row, group g's columns] = act(a[row, group g's columns] . w[g]^T) for w [G, N, K] on the tensor cores.
+    Without `listed` every group takes all rows of a, its K columns starting at g * a_group_stride, and writes its N
+    columns at g * o_group_stride of out's rows (one small matrix per head).  listed = (rows, group_off, tile_off) as
+    `group_rows` makes them: group g owns rows[group_off[g] : group_off[g + 1]]; it reads row rows[r] // a_div of a
+    and writes row rows[r] of out (routed experts)."""
+    G, N, K = w.shape
+    if a.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous() or not grouped_gemm_takes(a, w, a_group_stride):
+        raise KernelError("grouped_gemm: bfloat16 operands with unit column strides, rows and groups on 16-byte boundaries")
+    rows, group_off, tile_off = listed if listed is not None else (None, None, None)
+    fn = _fn("grouped_gemm", "lq_grouped_gemm", [c_void_p, c_long, c_long, c_int, c_void_p, c_long, c_void_p, c_int, c_long, c_long,
+                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(a), a.stride(0), a_group_stride, a_div, _p(w), N * K, _p(out), dtype_code(out), out.stride(0), o_group_stride,
+              _p(rows), _p(group_off), _p(tile_off), rows.numel() if rows is not None else 0, G, a.shape[0], N, K, MOE_ACTS[act],
+              _stream()), "grouped_gemm", 1, "grouped_gemm:listed" if listed is not None else "grouped_gemm:uniform")
+    return out
+
+
+def group_rows(ids: torch.Tensor, G: int) -> tuple:
+    """ids int32 [n], each in [0, G) -> (rows [n]: the indices 0 .. n-1 group by group, group_off [G + 1], tile_off [G + 1]),
+    made on the device."""
+    n = ids.numel()
+    rows = torch.empty(n, dtype=torch.int32, device=ids.device)
+    group_off = torch.empty(G + 1, dtype=torch.int32, device=ids.device)
+    tile_off = torch.empty(G + 1, dtype=torch.int32, device=ids.device)
+    fn = _fn("grouped_gemm", "lq_group_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_p(_contig(ids, "ids")), n, G, _p(rows), _p(group_off), _p(tile_off), _stream()), "group_rows")
+    return rows, group_off, tile_off
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, accumulate: bool = True,
+                shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
+    """x[t] (+)= sum_j weights[t, j] y[t * top + j] (+ sigmoid(shared_gate[t]) * shared[t]); y float32 [T * top, D]."""
+    T, top = weights.shape
+    D = y.shape[1]
+    if y.dtype != torch.float32 or tuple(y.shape) != (T * top, D) or not y.is_contiguous() or tuple(x.shape) != (T, D):
+        raise KernelError("moe_combine: float32 rows [T * top, D] and [T, D]")
+    fn = _fn("grouped_gemm", "lq_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                c_void_p])
+    _check(fn(_p(y), _p(_contig(weights, "weights")), _p(shared), _p(shared_gate),
+              shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), T, top, D, _stream()),
+           "moe_combine")
+    return x
 
 
 # ------------------------------------------------------------------ routed feed-forward

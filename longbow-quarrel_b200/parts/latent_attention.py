@@ -40,7 +40,7 @@ class LatentAttention(Mixer):
 
     @property
     def kernel_libraries(self):
-        return ("latent_attn", "latent_attn_tc") if self.runtime.dtype == torch.bfloat16 else ("latent_attn",)
+        return ("latent_attn", "latent_attn_tc", "grouped_gemm") if self.runtime.dtype == torch.bfloat16 else ("latent_attn",)
 
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, head_dim: int, rot_dim: int, value_dim: int,
                  q_rank: int, kv_rank: int, scale: float, eps: float, position: PartSpec | None = None,
@@ -59,7 +59,8 @@ class LatentAttention(Mixer):
         self.w_down: linear.LinearWeight | None = None
         self.w_uq: linear.LinearWeight | None = None
         self.w_o: linear.LinearWeight | None = None
-        self.w_uk = self.w_uv = self.g_q = self.g_kv = None
+        self.w_uk = self.w_uv = self.w_uk_t = self.w_uv_t = self.g_q = self.g_kv = None
+        self.tc_heads = False
 
     def cache_need(self):
         return KVNeed(1, self.R + self.dr, self.window, values=False)
@@ -98,6 +99,11 @@ class LatentAttention(Mixer):
         # Per head: W_uk,h as stored is [dim, R] = [K, N] for q -> latent; W_uv,h [vdim, R] is turned to [R, vdim].
         self.w_uk = tensors[n["uk"]].reshape(H, self.dn, self.R).contiguous()
         self.w_uv = tensors[n["uv"]].reshape(H, self.dv, self.R).transpose(1, 2).contiguous()
+        # The tensor-core products read every head's matrix as [outputs, inputs].
+        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()
+        self.w_uv_t = tensors[n["uv"]].reshape(H, self.dv, self.R).contiguous()
+        self.tc_heads = (self.runtime.dtype == torch.bfloat16 and self.w_uk.dtype == torch.bfloat16 and self.dn % 8 == 0
+                         and (self.dn + self.dr) % 8 == 0 and self.R % 8 == 0)
 
     def _splits(self, ctx: StepContext, blocks_per_token: int, places_per_sm: int = 1) -> int:
         """Slices per row for a step of single tokens: as many as fill the multiprocessors, none shorter than
@@ -109,18 +115,20 @@ class LatentAttention(Mixer):
         return max(1, min(places_per_sm * ops.sm_count(self.runtime.device) // blocks, reach // MIN_KEYS_PER_SLICE, 32))
 
     def _attend(self, wide, pages, ctx: StepContext, cache_view):
-        """The weighted means of latent rows, float32 [T, H, R]: on the tensor cores where the cache allows it."""
+        """The weighted means of latent rows [T, H, R]: on the tensor cores where the cache allows it (bfloat16 rows out
+        where the per-head products that follow run there too), else float32."""
         H, R = self.H, self.R
+        more = {"out_dtype": torch.bfloat16} if self.tc_heads else {}
         if ops.latent_attention_tc_takes(pages, cache_view.page_size):
             chunks = -(-R // (64 if R <= 64 else 128 if R <= 128 else 256))
             if ctx.decode:
                 return ops.latent_attention_tc(wide, pages, cache_view.page_table, ctx.slots, H, R, cache_view.page_size,
                                                self.scale, self.window, tok_pos=ctx.tok_pos, tok_seq=ctx.tok_seq,
-                                               splits=self._splits(ctx, -(-H // 64) * chunks, 2))
+                                               splits=self._splits(ctx, -(-H // 64) * chunks, 2), **more)
             flat = ctx.extra.get(f"latent_blocks{ops.latent_tc_tokens(H)}")
             if flat is not None and flat.numel():
                 return ops.latent_attention_tc(wide, pages, cache_view.page_table, ctx.slots, H, R, cache_view.page_size,
-                                               self.scale, self.window, blocks=tuple(flat.view(4, -1)))
+                                               self.scale, self.window, blocks=tuple(flat.view(4, -1)), **more)
         return ops.latent_attention(wide, pages, cache_view.page_table, ctx.tok_pos, ctx.tok_seq, ctx.slots, H, R,
                                     cache_view.page_size, self.scale, self.window, self._splits(ctx, -(-H // 8)))
 
@@ -136,14 +144,21 @@ class LatentAttention(Mixer):
         pages = cache_view.k_pages[:, 0]                             # one kv head: [pages, page_size, R + dr]
         ops.latent_kv_store(down, 0, R, self.g_kv, self.eps, cos, sin, self.rot, ctx.tok_pos, ctx.tok_seq, ctx.slots,
                             cache_view.page_table, pages, R, dr, cache_view.page_size)
-        q = linear.linear(cq, self.w_uq, torch.float32)              # [T, H (dn + dr)]
+        q = linear.linear(cq, self.w_uq, act if self.tc_heads else torch.float32)     # [T, H (dn + dr)]
         wide = torch.empty((T, H, R + dr), dtype=torch.float32, device=q.device)
         wide2 = wide.view(T, H * (R + dr))
-        ops.head_matmul(q, dn + dr, 0, self.w_uk, wide2, R + dr, 0)              # W_uk,h^T q_h
+        if self.tc_heads and ops.grouped_gemm_takes(q, self.w_uk_t, dn + dr):
+            ops.grouped_gemm(q, self.w_uk_t, wide2, a_group_stride=dn + dr, o_group_stride=R + dr)      # W_uk,h^T q_h
+        else:
+            ops.head_matmul(q, dn + dr, 0, self.w_uk, wide2, R + dr, 0)
         ops.rope_tail(q, dn + dr, dn, wide2, R + dr, R, cos, sin, self.rot, ctx.tok_pos, H, dr)
         mean = self._attend(wide, pages, ctx, cache_view)
         out = torch.empty((T, H * dv), dtype=act, device=q.device)
-        ops.head_matmul(mean.view(T, H * R), R, 0, self.w_uv, out, dv, 0)        # W_uv,h (sum_j p_j c_j)
+        mean = mean.view(T, H * R)
+        if mean.dtype == torch.bfloat16 and ops.grouped_gemm_takes(mean, self.w_uv_t, R):
+            ops.grouped_gemm(mean, self.w_uv_t, out, a_group_stride=R, o_group_stride=dv)                  # W_uv,h (sum_j p_j c_j)
+        else:
+            ops.head_matmul(mean, R, 0, self.w_uv, out, dv, 0)
         if self.gate is not None:
             ops.gate_mul(out, down[:, R + dr:], "sigmoid")
         if residual is None:

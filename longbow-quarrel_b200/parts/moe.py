@@ -8,8 +8,10 @@
 
 The experts have no gate and no bias.  A shared expert (a `dense_mlp` of its own size) runs for every
 token behind one sigmoid number per token.  The router's logits and the shared expert's gate come
-from one 32-bit product; choice and weights are one kernel, the experts' two products one kernel
-each (`csrc/moe.cu`), the second of which also adds the shared expert's rows and joins the stream.
+from one 32-bit product; choice and weights are one kernel.  Few tokens (a decode step): the experts' two
+products are one kernel each that streams every token's own experts (`csrc/moe.cu`), the second of which also
+adds the shared expert's rows and joins the stream.  Many tokens (a prompt, bfloat16): the (token, choice) pairs
+are sorted by expert on the device and each product is one grouped tensor-core launch (`csrc/grouped_gemm.cu`).
 Every kernel reads the chosen experts from device memory, so a step can be captured and replayed.
 """
 from __future__ import annotations
@@ -26,7 +28,12 @@ from .spec import PartSpec
 @register_part("ffn", "routed_experts")
 class RoutedExperts(FeedForward):
     graph_safe = True
-    kernel_libraries = ("moe", "recurrent")          # `recurrent` holds the 32-bit product for weights of few rows
+    GROUPED_FROM = 256       # (token, choice) pairs from which the experts' products run as grouped tensor-core products
+
+    @property
+    def kernel_libraries(self):
+        # `recurrent` holds the 32-bit product for weights of few rows (the router).
+        return ("moe", "recurrent", "grouped_gemm") if self.runtime.dtype == torch.bfloat16 else ("moe", "recurrent")
 
     def __init__(self, runtime: Runtime, hidden_size: int, n_experts: int, top: int, expert_size: int,
                  activation: str = "gelu", groups: int = 1, keep_groups: int = 1, route_scale: float = 1.0,
@@ -76,9 +83,20 @@ class RoutedExperts(FeedForward):
     def forward(self, h, ctx: StepContext, residual):
         z = ops.small_proj(h, self.w_route)                          # float32 [T, E (+ 1)]
         ids, weights = ops.moe_route(z, self.E, self.groups, self.keep, self.top, self.route_scale)
-        u = ops.moe_up(h, self.w_up, ids, self.activation)
         shared = self.shared.forward(h, ctx, None) if self.shared is not None else None
         gate = z[:, self.E] if self.shared is not None else None
+        T = h.shape[0]
+        if T * self.top >= self.GROUPED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
+            # Many tokens: the pairs sorted by expert (on the device), each expert's rows as tiles of a tensor-core product.
+            listed = ops.group_rows(ids.view(-1), self.E)
+            u = torch.empty((T * self.top, self.F), dtype=h.dtype, device=h.device)
+            ops.grouped_gemm(h, self.w_up, u, listed=listed, a_div=self.top, act=self.activation)
+            y = torch.empty((T * self.top, self.D), dtype=torch.float32, device=h.device)
+            ops.grouped_gemm(u, self.w_down, y, listed=listed)
+            out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
+            ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate)
+            return None if residual is not None else out
+        u = ops.moe_up(h, self.w_up, ids, self.activation)
         if residual is None:
             out = torch.empty((h.shape[0], self.D), dtype=torch.float32, device=h.device)
             return ops.moe_down(u, self.w_down, ids, weights, out, accumulate=False, shared=shared, shared_gate=gate)

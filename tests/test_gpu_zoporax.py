@@ -237,17 +237,19 @@ def test_the_command_line_generates_with_a_zoporax_folder(tmp_path):
 
 
 def test_random_weights_from_a_configuration_and_the_kernels_that_served_it():
-    """Engine.from_config builds the design from a dict with config.json's keys; a prompt and decoded tokens go
-    through the design's own kernels (and the decoded rows' keys are cut into slices)."""
+    """Engine.from_config builds the design from a dict with config.json's keys; in bfloat16 a prompt of a hundred tokens
+    and decoded tokens go through the design's tensor-core kernels (attention over latent rows, per-head matrices and
+    the experts of the prompt as grouped products) and, for the decoded tokens' experts, the streaming kernels."""
     from longbow_quarrel_b200.engine import Engine
     from longbow_quarrel_b200.kernels import ops
     from longbow_quarrel_b200.sampling import SamplingParams
     eng = Engine.from_config(CONFIGS["wide"], seed=3, max_tokens=512, max_batch=2)
     before = ops.launches_by_name()
-    out = eng.generate([[1, 2, 3], [4]], max_new_tokens=5, sampling=SamplingParams(temperature=0.0), stop_ids=[])
+    out = eng.generate([list(range(1, 101)), [4]], max_new_tokens=5, sampling=SamplingParams(temperature=0.0), stop_ids=[])
     ran = ops.launches_since(before)
     assert [len(o) for o in out] == [5, 5]
-    for kernel in ("latent_attention", "latent_kv_store", "head_matmul", "rope_tail", "linear_scan", "linear_scan:single",
-                   "moe_route", "moe_up", "moe_down", "gated_act", "add_bias", "small_proj", "head_norm_gate"):
+    for kernel in ("latent_attention_tc", "latent_kv_store", "grouped_gemm:uniform", "grouped_gemm:listed", "group_rows",
+                   "moe_combine", "rope_tail", "linear_scan", "linear_scan:single", "moe_route", "moe_up", "moe_down",
+                   "gated_act", "add_bias", "small_proj", "head_norm_gate"):
         assert ran.get(kernel, 0) >= 1, (kernel, ran)
     eng.close()

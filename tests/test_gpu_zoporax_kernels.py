@@ -397,3 +397,60 @@ def test_tensor_core_attention_finds_the_key_that_outweighs_all_others_up_to_the
         for t, sees in enumerate([True, win is None, win is None]):
             closeness = _rel(out[t, 0], stored[planted, :R])
             assert (closeness < 1e-2) == sees, (win, pos1[t], closeness)
+
+
+# ------------------------------------------------------------------ many small products in one launch
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,K,N", [(1, 1, 8, 5), (13, 3, 24, 40), (70, 8, 32, 96), (200, 2, 304, 130), (8, 16, 128, 512)])
+def test_one_matrix_per_head_on_the_tensor_cores(out_dtype, T, H, K, N):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + K)
+    src = torch.randn(T, H * (K + 8), generator=g).to(torch.bfloat16)
+    w = (torch.randn(H, N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    out = torch.full((T, H * (N + 3) + 2), 7.0, dtype=out_dtype, device=DEV)
+    ops.grouped_gemm(src.to(DEV), w.to(DEV), out, a_group_stride=K + 8, o_group_stride=N + 3)
+    ref = torch.einsum("thk,hnk->thn", src.double().reshape(T, H, K + 8)[:, :, :K], w.double())
+    got = out[:, :H * (N + 3)].reshape(T, H, N + 3)
+    assert _rel(got[:, :, :N], ref) < (2e-6 if out_dtype == torch.float32 else 4e-3)
+    assert (got[:, :, N:] == 7.0).all() and (out[:, H * (N + 3):] == 7.0).all()
+
+
+@pytest.mark.parametrize("T,E,top,D,F", [(40, 3, 3, 40, 16), (137, 8, 2, 64, 24), (300, 16, 3, 104, 56), (300, 6, 1, 128, 48), (64, 160, 6, 64, 32)])
+def test_the_experts_products_as_grouped_products(T, E, top, D, F):
+    """The (token, choice) pairs sorted by expert on the device, both products as grouped launches, the combination: against
+    the same sums in float64 (and so against the kernels that stream every token's own experts)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + E)
+    h = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    w_up = (torch.randn(E, F, D, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+    w_down = (torch.randn(E, D, F, generator=g) / math.sqrt(F)).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    if E > 4:
+        ids[ids == 1] = 2 if top == 1 else ids[ids == 1]    # with one choice per token: an expert that nobody chose
+    weights = torch.rand(T, top, generator=g)
+    shared = torch.randn(T, D, generator=g)
+    zs = torch.randn(T, generator=g)
+    x0 = torch.randn(T, D, generator=g)
+    rows, group_off, tile_off = ops.group_rows(ids.to(DEV).view(-1), E)
+    counts = torch.bincount(ids.view(-1).long(), minlength=E)
+    assert group_off.cpu().tolist() == [0] + counts.cumsum(0).tolist()
+    assert tile_off.cpu().tolist() == [0] + ((counts + 63) // 64).cumsum(0).tolist()
+    listed = rows.cpu().long()
+    assert sorted(listed.tolist()) == list(range(T * top))
+    assert (ids.view(-1)[listed] == torch.repeat_interleave(torch.arange(E), counts).to(torch.int32)).all()
+    u = torch.empty(T * top, F, dtype=torch.bfloat16, device=DEV)
+    ops.grouped_gemm(h.to(DEV), w_up.to(DEV), u, listed=(rows, group_off, tile_off), a_div=top, act="gelu")
+    pre = torch.einsum("tjfd,td->tjf", w_up.double()[ids.long()], h.double())
+    assert _rel(u.reshape(T, top, F), 0.5 * pre * (1 + torch.erf(pre / math.sqrt(2.0)))) < 4e-3
+    y = torch.empty(T * top, D, dtype=torch.float32, device=DEV)
+    ops.grouped_gemm(u, w_down.to(DEV), y, listed=(rows, group_off, tile_off))
+    y_ref = torch.einsum("tjdf,tjf->tjd", w_down.double()[ids.long()], u.double().cpu().reshape(T, top, F))
+    assert _rel(y.reshape(T, top, D), y_ref) < 2e-6
+    x = x0.clone().to(DEV)
+    ops.moe_combine(y, weights.to(DEV), x, True, shared.to(DEV), zs.to(DEV))
+    ref = x0.double() + (weights.double()[:, :, None] * y_ref).sum(1) + torch.sigmoid(zs.double())[:, None] * shared.double()
+    assert _rel(x, ref) < 2e-6
+    # the streaming kernels make the same rows
+    u2 = ops.moe_up(h.to(DEV), w_up.to(DEV), ids.to(DEV), "gelu")
+    assert _rel(u2, u.reshape(T, top, F)) < 4e-3
