@@ -136,7 +136,7 @@ template <int BN, int STAGES, int EPI, int AROWS>
 __global__ void __launch_bounds__(N_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, int staged, void* Cout, const float* residual, int M, int N, int K, int splits,
-               int plane_rows, const QkvArgs qkv) {
+               int plane_rows, const QkvArgs qkv, const int* __restrict__ tile_group) {
     extern __shared__ uint8_t smem_raw[];
     constexpr bool STAGED = StagedEpilogue<BN, EPI, AROWS>::value;
     using S = Smem<BN, STAGES, AROWS, STAGED>;
@@ -178,6 +178,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x) {
                 const int tile = piece / splits, range = piece % splits;
                 const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                // Grouped products: the rows of a tile all belong to one group, whose weight is rows
+                // group * N .. of W; a tile without a group (padding behind the last one) is left out by all roles.
+                const int group = tile_group ? tile_group[tile % m_tiles] : 0;
+                if (group < 0) continue;
                 const int kb_lo = (int)((long)n_kb * range / splits), kb_hi = (int)((long)n_kb * (range + 1) / splits);
                 for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -185,7 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t full = smem_u32(&sm.full[s]);
                     mbar_expect_tx(full, STAGE_BYTES);
                     tma_load_2d(smem_u32(sm.a[s]), &map_a, kb * BK, m0, full);
-                    tma_load_2d(smem_u32(sm.b[s]), &map_b, kb * BK, n0, full);
+                    tma_load_2d(smem_u32(sm.b[s]), &map_b, kb * BK, n0 + group * N, full);
                 }
             }
             if (!ok) {
@@ -204,6 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
+                if (tile_group && tile_group[(piece / splits) % m_tiles] < 0) { --t; continue; }
                 const int range = piece % splits;
                 const int kb_lo = (int)((long)n_kb * range / splits), kb_hi = (int)((long)n_kb * (range + 1) / splits);
                 const uint32_t acc = t & 1;
@@ -232,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         for (int piece = blockIdx.x; piece < total && ok; piece += gridDim.x, ++t) {
             const int tile = piece / splits, range = piece % splits;
+            if (tile_group && tile_group[tile % m_tiles] < 0) { --t; continue; }
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             void* dst = splits > 1 ? (void*)((float*)Cout + (size_t)range * plane_rows * N) : Cout;
             const uint32_t acc = t & 1;
@@ -391,7 +397,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 template <int BN, int STAGES, int EPI, int AROWS>
 int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* residual, int M, int N, int K,
-               int n_sms, int splits, const QkvArgs& qkv, cudaStream_t stream) {
+               int n_sms, int splits, const QkvArgs& qkv, cudaStream_t stream, const int* tile_group = nullptr) {
     constexpr bool STAGED = StagedEpilogue<BN, EPI, AROWS>::value;
     constexpr size_t smem = sizeof(Smem<BN, STAGES, AROWS, STAGED>) + 1024;
     static_assert(smem <= 232448, "more shared memory than a block may have");
@@ -411,7 +417,7 @@ int launch_epi(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const floa
     if constexpr (STAGED)
         staged = staged_map<EPI>(&mc, C, residual, splits > 1 ? (long)splits * plane_rows : M, EPI == EPI_SWIGLU ? N / 2 : N);
     return launch_pdl(gemm_tc_kernel<BN, STAGES, EPI, AROWS>, dim3(grid), dim3(N_THREADS), smem, stream, ma, mb, mc, staged, C, residual,
-                      M, N, K, splits, plane_rows, qkv);
+                      M, N, K, splits, plane_rows, qkv, tile_group);
 }
 
 // ALL: every epilogue; otherwise only the two that products with many columns have (SwiGLU, float32 store).
@@ -540,6 +546,22 @@ LQ_EXPORT int lq_gemm_tc_qkv(const void* X, const void* W, void* q_out, int M, i
     const QkvArgs a{cos_t, sin_t, tok_pos, tok_seq, slots, page_table, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
                     pt_stride, H, Hkv, hd, page_size};
     return gemm_tc_dispatch(X, W, q_out, nullptr, M, (H + 2 * Hkv) * hd, K, EPI_QKV, scratch, a, stream);
+}
+
+// Many products in one launch: the rows of A [M, K] come in tiles of 128 that each belong to one group (tile_group
+// [M / 128] on the device: the group, or -1 for a tile to leave out), and a tile of group g is multiplied with rows
+// g * N .. (g + 1) * N of W [G * N, K].  C [M, N] bfloat16 (out_f32 0) or float32 (1).  M a multiple of 128.
+LQ_EXPORT int lq_gemm_tc_grouped(const void* A, const void* W, void* C, int out_f32, int M, int N, int K, int G,
+                                 const int* tile_group, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || G <= 0) return LQ_OK;
+    if (M % BM || K <= 0 || K % 8 || !tile_group || (((uintptr_t)A | (uintptr_t)W) & 15)) return LQ_BAD_SIZE;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, M, K, BM);
+    if (rc != LQ_OK) return rc;
+    rc = make_map(&mb, W, G * N, K, 256);
+    if (rc != LQ_OK) return rc;
+    if (out_f32) return launch_epi<256, 4, EPI_F32, BM>(ma, mb, C, nullptr, M, N, K, sm_count(), 1, QkvArgs{}, stream, tile_group);
+    return launch_epi<256, 4, EPI_BF16, BM>(ma, mb, C, nullptr, M, N, K, sm_count(), 1, QkvArgs{}, stream, tile_group);
 }
 
 LQ_EXPORT int lq_gemm_tc_splits(int M, int N, int K) {

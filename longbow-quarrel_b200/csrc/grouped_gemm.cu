@@ -9,14 +9,23 @@
 //             experts: the (token, choice) pairs sorted by expert; A's row is rows[r] / a_div, so that the `top`
 //             choices of a token read the token's one input row; out's row is rows[r]).  lq_group_rows makes the list
 //             on the device from the chosen experts, so that nothing of a step waits for the host.
-// A block makes a 64 x 128 tile of one group: 2 x 2 warps of 32 x 64, operands through shared memory in steps of
-// 32 along K (cp.async, two stages, rows padded against bank conflicts).
+// A block makes a 64 x BN tile of one group (BN 256 for wide outputs, else 128): 2 x BN/64 warps of 32 x 64, operands
+// through shared memory in steps of 32 along K (cp.async, two stages, rows padded against bank conflicts).  Measured
+// on B200 with 64 x 128 tiles: deeper pipelines and longer steps ran slower (fewer blocks fit a multiprocessor); the
+// bound is the traffic from L2 into shared memory, which a wider tile lowers per product.
 #include "common.cuh"
 #include <math_constants.h>
 
 namespace {
 
-constexpr int BM = 64, BN = 128, BK = 32, PAD = 8, NT = 128, LDS = BK + PAD;
+#ifndef GG_BK
+#define GG_BK 32
+#endif
+#ifndef GG_STAGES
+#define GG_STAGES 2
+#endif
+constexpr int BM = 64, BK = GG_BK, PAD = 8, LDS = BK + PAD, STAGES = GG_STAGES;
+constexpr size_t gg_smem_bytes(int BN) { return (size_t)STAGES * (BM + BN) * LDS * 2; }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     int bytes = valid ? 16 : 0;
@@ -60,13 +69,17 @@ struct GroupedArgs {
     int G, M, N, K, act;
 };
 
-template <typename TO>
-__global__ void __launch_bounds__(NT) grouped_gemm_kernel(GroupedArgs a) {
-    __shared__ __align__(16) __nv_bfloat16 sa[2][BM][LDS];
-    __shared__ __align__(16) __nv_bfloat16 sb[2][BN][LDS];
+template <typename TO, int BN>
+__global__ void __launch_bounds__(BN) grouped_gemm_kernel(GroupedArgs a) {
+    constexpr int WN = BN / 64, NT = 2 * WN * 32;
+    extern __shared__ __align__(16) uint8_t gg_smem[];
+    typedef __nv_bfloat16 (*TileA)[BM][LDS];
+    typedef __nv_bfloat16 (*TileB)[BN][LDS];
+    TileA sa = reinterpret_cast<TileA>(gg_smem);
+    TileB sb = reinterpret_cast<TileB>(gg_smem + (size_t)STAGES * BM * LDS * 2);
     __shared__ int s_rows[BM];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
-    const int wm = warp >> 1, wn = warp & 1;
+    const int wm = warp / WN, wn = warp % WN;
     pdl_launch_dependents();
     pdl_wait();
     // Which group, and which of its row tiles.
@@ -114,14 +127,16 @@ __global__ void __launch_bounds__(NT) grouped_gemm_kernel(GroupedArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
     const int steps = (K + BK - 1) / BK;
-    load(0, 0);
-    cp_async_commit();
-    for (int s = 0; s < steps; ++s) {
-        const int stage = s & 1;
-        if (s + 1 < steps) load((s + 1) * BK, stage ^ 1);
+    for (int p = 0; p < STAGES - 1; ++p) {
+        if (p < steps) load(p * BK, p);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
+    }
+    for (int s = 0; s < steps; ++s) {
+        const int stage = s % STAGES;
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                          // step s has landed, and everyone is done with the stage that is loaded next
+        if (s + STAGES - 1 < steps) load((s + STAGES - 1) * BK, (s + STAGES - 1) % STAGES);
+        cp_async_commit();
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
             uint32_t af[2][4];
@@ -142,7 +157,6 @@ __global__ void __launch_bounds__(NT) grouped_gemm_kernel(GroupedArgs a) {
                 }
             }
         }
-        __syncthreads();
     }
     TO* out = (TO*)a.out + (long long)g * a.o_group_stride;
 #pragma unroll
@@ -190,6 +204,68 @@ __global__ void __launch_bounds__(1024) group_rows_kernel(const int* __restrict_
     for (int i = threadIdx.x; i < n; i += blockDim.x) rows[atomicAdd(&cursor[ids[i]], 1)] = i;
 }
 
+// The same list with every group's rows padded to whole tiles of `tile` rows, for a product whose row tiles each
+// belong to one group: src [cap] = the index that stands at each padded place (-1: padding), dst [n] = the place of
+// each index, tile_group [cap / tile] = each tile's group (-1 behind the last).  cap = (ceil(n / tile) + G) * tile holds every case.
+__global__ void __launch_bounds__(1024) group_rows_padded_kernel(const int* __restrict__ ids, int n, int G, int tile, int cap,
+                                                                 int* __restrict__ src, int* __restrict__ dst,
+                                                                 int* __restrict__ tile_group) {
+    pdl_launch_dependents();
+    extern __shared__ int sm[];
+    int* count = sm;
+    int* cursor = sm + G;
+    pdl_wait();
+    for (int g = threadIdx.x; g < G; g += blockDim.x) count[g] = 0;
+    for (int i = threadIdx.x; i < cap; i += blockDim.x) src[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int g = 0; g < G; ++g) {
+            cursor[g] = at;
+            const int tiles = (count[g] + tile - 1) / tile;
+            for (int k = 0; k < tiles; ++k) tile_group[at / tile + k] = g;
+            at += tiles * tile;
+        }
+        for (int k = at / tile; k < cap / tile; ++k) tile_group[k] = -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int p = atomicAdd(&cursor[ids[i]], 1);
+        src[p] = i;
+        dst[i] = p;
+    }
+}
+
+// out[p, :] = a[src[p] / div, :] (zeros where src[p] < 0): the rows of a product's input in the padded order.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ a, const int* __restrict__ src, int div,
+                                                          uint4* __restrict__ out, int cap, int row16) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.x, s = src[p];
+    for (int i = threadIdx.x; i < row16; i += 256)
+        out[(size_t)p * row16 + i] = s >= 0 ? a[(size_t)(s / div) * row16 + i] : make_uint4(0, 0, 0, 0);
+}
+
+// x[t, :] (+)= sum_j weights[t, j] y[place(t * top + j), :] ... with `place` = dst of the padded order (null: the pair itself)
+__global__ void __launch_bounds__(256) moe_combine_at_kernel(const float* __restrict__ y, const int* __restrict__ place,
+                                                             const float* __restrict__ weights, const float* __restrict__ shared,
+                                                             const float* __restrict__ zs, int zs_stride, float* __restrict__ x,
+                                                             int accumulate, int top, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
+    for (int d = threadIdx.x; d < D; d += 256) {
+        float s = 0.f;
+        for (int j = 0; j < top; ++j) s = fmaf(weights[(size_t)t * top + j], y[(size_t)place[t * top + j] * D + d], s);
+        if (shared) s = fmaf(sg, shared[(size_t)t * D + d], s);
+        float* o = x + (size_t)t * D + d;
+        *o = accumulate ? *o + s : s;
+    }
+}
+
 // x[t, :] (+)= sum_j weights[t, j] y[t * top + j, :] (+ sigmoid(zs[t]) * shared[t, :]), the choices added in their order.
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
                                                           const float* __restrict__ shared, const float* __restrict__ zs,
@@ -229,10 +305,35 @@ LQ_EXPORT int lq_grouped_gemm(const void* A, long long lda, long long a_group_st
     if (rows ? (!group_off || !tile_off || n_listed <= 0) : M <= 0) return LQ_BAD_SIZE;
     GroupedArgs a{(const __nv_bfloat16*)A, lda, a_group_stride, a_div, (const __nv_bfloat16*)W, w_group_stride, out, ldo,
                   o_group_stride, rows, group_off, tile_off, G, M, N, K, act};
-    dim3 grid(rows ? lq_grouped_gemm_tiles(n_listed, G) : G * ((M + BM - 1) / BM), (N + BN - 1) / BN);
-    if (out_dtype == LQ_F32) return launch_pdl(grouped_gemm_kernel<float>, grid, dim3(NT), 0, stream, a);
-    if (out_dtype == LQ_BF16) return launch_pdl(grouped_gemm_kernel<__nv_bfloat16>, grid, dim3(NT), 0, stream, a);
+    const int row_tiles = rows ? lq_grouped_gemm_tiles(n_listed, G) : G * ((M + BM - 1) / BM);
+#define LQ_GO(TO, BN) do { \
+        cudaFuncSetAttribute(grouped_gemm_kernel<TO, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gg_smem_bytes(BN)); \
+        return launch_pdl(grouped_gemm_kernel<TO, BN>, dim3(row_tiles, (N + BN - 1) / BN), dim3(BN), gg_smem_bytes(BN), stream, a); } while (0)
+    if (out_dtype == LQ_F32) { if (N >= 256) LQ_GO(float, 256); LQ_GO(float, 128); }
+    if (out_dtype == LQ_BF16) { if (N >= 256) LQ_GO(__nv_bfloat16, 256); LQ_GO(__nv_bfloat16, 128); }
+#undef LQ_GO
     return LQ_BAD_DTYPE;
+}
+
+LQ_EXPORT int lq_group_rows_padded(const int* ids, int n, int G, int tile, int cap, int* src, int* dst, int* tile_group,
+                                   cudaStream_t stream) {
+    if (n <= 0 || G <= 0 || tile <= 0 || cap % tile || cap < ((n + tile - 1) / tile + G) * tile) return LQ_BAD_SIZE;
+    const size_t smem = 2 * (size_t)G * sizeof(int);
+    if (smem > 48 * 1024) return LQ_BAD_SIZE;
+    return launch_pdl(group_rows_padded_kernel, dim3(1), dim3(1024), smem, stream, ids, n, G, tile, cap, src, dst, tile_group);
+}
+
+// a [*, row_bytes] -> out [cap, row_bytes]; row_bytes a multiple of 16, both 16-byte aligned.
+LQ_EXPORT int lq_gather_rows(const void* a, const int* src, int div, void* out, int cap, int row_bytes, cudaStream_t stream) {
+    if (cap <= 0) return LQ_OK;
+    if (row_bytes % 16 || div < 1 || (((uintptr_t)a | (uintptr_t)out) & 15)) return LQ_BAD_SIZE;
+    return launch_pdl(gather_rows_kernel, dim3(cap), dim3(256), 0, stream, (const uint4*)a, src, div, (uint4*)out, cap, row_bytes / 16);
+}
+
+LQ_EXPORT int lq_moe_combine_at(const float* y, const int* place, const float* weights, const float* shared, const float* zs,
+                                int zs_stride, float* x, int accumulate, int T, int top, int D, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    return launch_pdl(moe_combine_at_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, shared, zs, zs_stride, x, accumulate, top, D);
 }
 
 LQ_EXPORT int lq_moe_combine(const float* y, const float* weights, const float* shared, const float* zs, int zs_stride, float* x,

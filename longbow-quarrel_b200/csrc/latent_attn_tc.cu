@@ -6,8 +6,10 @@
 // come in tiles of 32 cached rows (cp.async, padded rows); S = Q K^T and O += P V run on mma.sync m16n8k16 with
 // float32 accumulation, the softmax online in float32 as in attn_prefill.cu.  The values are the first R columns of
 // the very tile that served as keys, read transposed.  A warp cannot hold 16 x R accumulators for a latent of
-// several hundred numbers, so the R columns are cut into chunks of CW (64, 128 or 256) that separate blocks
-// accumulate, each making the scores again: for R = 512, Dk = 576 that is 1.5 times the products of one pass.
+// several hundred numbers, so the R columns are cut into chunks of CW (64, 128 or 256), each accumulated by its own
+// group of four warps that makes the scores again: for R = 512, Dk = 576 that is 1.5 times the products of one
+// pass.  Two such groups share a block, and with it the queries and the key tiles in shared memory (two tiles, the
+// next one on its way while the current one is multiplied).
 //
 // Prompts and portions: a work list made on the host (sequence, first packed row, tokens, first position), the
 // blocks with the most keys first.  Steps of one token per sequence: a block per token, the token's keys cut into
@@ -68,18 +70,20 @@ struct LatentArgs {
     float scale_log2;
 };
 
-// CW: value columns that a block accumulates.
-template <int CW>
-__global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_kernel(LatentArgs a) {
+// CW: value columns that a group of four warps accumulates; NCH: groups (chunks of columns) of a block.
+template <int CW, int NCH>
+__global__ void __launch_bounds__(NT * NCH, 1) latent_attention_tc_kernel(LatentArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int H = a.H, R = a.R, Dk = a.Dk;
     const int DKP = (Dk + 15) & ~15;                                  // k16 steps cover the padded width (zeros beyond Dk)
     const int LD = max(DKP, a.chunks * CW) + PAD;                     // the value columns of the last chunk stay inside a row
     __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][DKP + PAD]
-    const int LQ = DKP + PAD;
-    __nv_bfloat16* sk = sq + BM * LQ;                                 // [BN][LD]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int blk = blockIdx.x, hb = blockIdx.y % a.head_blocks, chunk = blockIdx.y / a.head_blocks, split = blockIdx.z;
+    const int LQ = DKP + PAD;                                         // the key tiles follow the queries: [2][BN][LD]
+    constexpr int THREADS = NT * NCH;
+    const int tid = threadIdx.x, warp = (tid >> 5) & 3, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int blk = blockIdx.x, hb = blockIdx.y % a.head_blocks, split = blockIdx.z;
+    const int chunk = (blockIdx.y / a.head_blocks) * NCH + (tid >> 7);
+    const bool chunk_live = chunk < a.chunks;
     const int Hb = min(H - hb * BM, BM), h0 = hb * BM;                // heads of this block
     const int TB = BM / Hb;                                           // tokens whose heads fit into the block's rows
     const int c0 = chunk * CW;
@@ -96,7 +100,7 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
     const int tile_lo = t_lo + (int)((long long)split * t_n / a.splits), tile_hi = t_lo + (int)((long long)(split + 1) * t_n / a.splits);
 
     // ---- the block's queries: row r is head h0 + r % Hb of token r / Hb
-    for (int i = tid; i < BM * (DKP / 2); i += NT) {
+    for (int i = tid; i < BM * (DKP / 2); i += THREADS) {
         const int r = i / (DKP / 2), c = (i % (DKP / 2)) * 2;
         const int tl = r / Hb, hl = r % Hb;
         float v0 = 0.f, v1 = 0.f;
@@ -107,9 +111,10 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
         }
         *reinterpret_cast<uint32_t*>(sq + r * LQ + c) = pack_bf16(v0, v1);
     }
-    auto load_keys = [&](int tile) {
+    auto load_keys = [&](int tile, int stage) {
         const int kb = tile * BN;
-        for (int i = tid; i < BN * (DKP / 8); i += NT) {
+        __nv_bfloat16* sk = sq + BM * LQ + stage * BN * LD;
+        for (int i = tid; i < BN * (DKP / 8); i += THREADS) {
             const int r = i / (DKP / 8), c = (i % (DKP / 8)) * 8, kp = kb + r;
             const bool ok = kp <= key_last && c < Dk;
             const __nv_bfloat16* src = a.pages;
@@ -129,17 +134,21 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
     const bool row0ok = r0 / Hb < n_tok, row1ok = r1 / Hb < n_tok;
     const int prow0 = pos0 + r0 / Hb, prow1 = pos0 + r1 / Hb;
     const int w_tl_lo = (warp * 16) / Hb, w_tl_hi = min((warp * 16 + 15) / Hb, n_tok - 1);
-    const bool warp_live = w_tl_lo < n_tok;
+    const bool warp_live = w_tl_lo < n_tok && chunk_live;
     const int warp_pos_hi = pos0 + w_tl_hi;
     const int warp_key_lo = window > 0 ? max(0, pos0 + w_tl_lo - window + 1) : 0;
     const int kd = DKP / 16;
 
+    if (tile_lo < tile_hi) load_keys(tile_lo, 0);
+    cp_async_commit();
     for (int tile = tile_lo; tile < tile_hi; ++tile) {
-        __syncthreads();                                  // the tile before has been read (and the queries are written)
-        load_keys(tile);
+        const int stage = (tile - tile_lo) & 1;
+        __syncthreads();                                  // the other stage has been read (and the queries are written)
+        if (tile + 1 < tile_hi) load_keys(tile + 1, stage ^ 1);
         cp_async_commit();
-        cp_async_wait<0>();
+        cp_async_wait<1>();
         __syncthreads();
+        const __nv_bfloat16* sk = sq + BM * LQ + stage * BN * LD;
         const int kb = tile * BN;
         if (!warp_live || kb > warp_pos_hi || kb + BN <= warp_key_lo) continue;
         float s[4][4];
@@ -222,7 +231,7 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int r = half ? r1 : r0;
-        if (!(half ? row1ok : row0ok)) continue;
+        if (!(half ? row1ok : row0ok) || !chunk_live) continue;
         const size_t pair = (size_t)(row0 + r / Hb) * H + h0 + r % Hb;
         const float inv = half ? i1 : i0;
         if (whole && a.out_bf16) {
@@ -250,45 +259,56 @@ __global__ void __launch_bounds__(NT, CW <= 128 ? 3 : 2) latent_attention_tc_ker
     }
 }
 
-// One warp per (row, head): the slices' results combined in the order of the slices.
+// One block per (row, head): the slices' weights once, then a thread per value column, the slices added in their order.
 template <typename TO>
 __global__ void __launch_bounds__(128) latent_merge_tc_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                               TO* __restrict__ out, int n_pairs, int R, int splits) {
     pdl_launch_dependents();
     pdl_wait();
-    const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (pair >= n_pairs) return;
+    __shared__ float wgt[64];
+    __shared__ float inv_s;
+    const int pair = blockIdx.x, tid = threadIdx.x;
     const float* ml = part_ml + (size_t)pair * splits * 2;
-    float m = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) l += ml[2 * s] == -CUDART_INF_F ? 0.f : ml[2 * s + 1] * expf(ml[2 * s] - m);
-    const float inv = 1.f / l;
-    for (int d = lane; d < R; d += 32) {
+    if (tid < 32) {
+        float m = -CUDART_INF_F;
+        for (int s = tid; s < splits; s += 32) m = fmaxf(m, ml[2 * s]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = tid; s < splits; s += 32) {
+            const float w = ml[2 * s] == -CUDART_INF_F ? 0.f : expf(ml[2 * s] - m);
+            wgt[s] = w;
+            l += w * ml[2 * s + 1];
+        }
+        l = warp_sum(l);
+        if (tid == 0) inv_s = 1.f / l;
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int d = tid; d < R; d += 128) {
         float o = 0.f;
         for (int s = 0; s < splits; ++s)
-            if (ml[2 * s] != -CUDART_INF_F) o = fmaf(part_o[((size_t)pair * splits + s) * R + d], expf(ml[2 * s] - m), o);
+            if (wgt[s] != 0.f) o = fmaf(part_o[((size_t)pair * splits + s) * R + d], wgt[s], o);
         out[(size_t)pair * R + d] = from_f32<TO>(o * inv);
     }
 }
 
-template <int CW>
+template <int CW, int NCH>
 int launch(LatentArgs a, int n_blocks, int T, cudaStream_t stream) {
     a.chunks = (a.R + CW - 1) / CW;
     const int DKP = (a.Dk + 15) & ~15;
     const int LD = (DKP > a.chunks * CW ? DKP : a.chunks * CW) + PAD;
-    const size_t smem = ((size_t)BM * (DKP + PAD) + (size_t)BN * LD) * 2;
+    const size_t smem = ((size_t)BM * (DKP + PAD) + (size_t)2 * BN * LD) * 2;
     if (smem > 220 * 1024) return LQ_BAD_SIZE;
-    if (cudaFuncSetAttribute(latent_attention_tc_kernel<CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(latent_attention_tc_kernel<CW, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return lq_launch_status();
-    dim3 grid(n_blocks, a.head_blocks * a.chunks, a.splits);
-    int rc = launch_pdl(latent_attention_tc_kernel<CW>, grid, dim3(NT), smem, stream, a);
+    dim3 grid(n_blocks, a.head_blocks * ((a.chunks + NCH - 1) / NCH), a.splits);
+    int rc = launch_pdl(latent_attention_tc_kernel<CW, NCH>, grid, dim3(NT * NCH), smem, stream, a);
     if (rc != LQ_OK || a.splits == 1) return rc;
     const int n = T * a.H;
     if (a.out_bf16)
-        return launch_pdl(latent_merge_tc_kernel<__nv_bfloat16>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float*)a.part_o,
+        return launch_pdl(latent_merge_tc_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, (const float*)a.part_o,
                           (const float*)a.part_ml, reinterpret_cast<__nv_bfloat16*>(a.out), n, a.R, a.splits);
-    return launch_pdl(latent_merge_tc_kernel<float>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float*)a.part_o,
+    return launch_pdl(latent_merge_tc_kernel<float>, dim3(n), dim3(128), 0, stream, (const float*)a.part_o,
                       (const float*)a.part_ml, a.out, n, a.R, a.splits);
 }
 
@@ -306,13 +326,14 @@ LQ_EXPORT int lq_latent_attention_tc(const float* q, const void* pages, const in
                                      int n_blocks, int T, int H, int R, int Dk, int page_size, float scale, int window,
                                      int splits, cudaStream_t stream) {
     if (n_blocks <= 0) return LQ_OK;
-    if (Dk % 8 || R < 1 || R > Dk || page_size % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return LQ_BAD_SIZE;
+    if (Dk % 8 || R < 1 || R > Dk || page_size % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml)) || splits > 64) return LQ_BAD_SIZE;
     if (!qb_seq && (!tok_pos || !tok_seq)) return LQ_BAD_SIZE;
     if (out_dtype != LQ_F32 && out_dtype != LQ_BF16) return LQ_BAD_DTYPE;
     LatentArgs a{q, (const __nv_bfloat16*)pages, page_table, pt_stride, slots, qb_seq, qb_row, qb_rows, qb_pos, tok_pos, tok_seq,
                  (float*)out, part_o, part_ml, H, R, Dk, page_size, window, splits, (H + BM - 1) / BM, 1, out_dtype == LQ_BF16,
                  scale * 1.4426950408889634f};
-    if (R <= 64) return launch<64>(a, n_blocks, T, stream);
-    if (R <= 128) return launch<128>(a, n_blocks, T, stream);
-    return launch<256>(a, n_blocks, T, stream);
+    if (R <= 64) return launch<64, 1>(a, n_blocks, T, stream);
+    if (R <= 128) return launch<128, 1>(a, n_blocks, T, stream);
+    if (R <= 256) return launch<256, 1>(a, n_blocks, T, stream);
+    return launch<256, 2>(a, n_blocks, T, stream);
 }

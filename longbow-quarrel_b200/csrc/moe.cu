@@ -97,6 +97,39 @@ __device__ __forceinline__ float moe_act(float v, int act) {
     }
 }
 
+// sum_k x[k] * w[k] over a row of n numbers, by one warp (x float32 in shared memory).  bfloat16 rows whose length is a
+// multiple of 8 are read 16 bytes a lane at a time (rows then start on 16-byte boundaries), two loads in flight.
+__device__ __forceinline__ float row_dot(const float* __restrict__ x, const float* __restrict__ w, int n, int lane) {
+    float s = 0.f;
+    for (int k = lane; k < n; k += 32) s = fmaf(x[k], w[k], s);
+    return warp_sum(s);
+}
+__device__ __forceinline__ float dot8(const float* x, uint4 v, float s) {
+    const float4 a = *reinterpret_cast<const float4*>(x), b = *reinterpret_cast<const float4*>(x + 4);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const float2 w0 = __bfloat1622float2(p[0]), w1 = __bfloat1622float2(p[1]), w2 = __bfloat1622float2(p[2]), w3 = __bfloat1622float2(p[3]);
+    s = fmaf(a.x, w0.x, s); s = fmaf(a.y, w0.y, s); s = fmaf(a.z, w1.x, s); s = fmaf(a.w, w1.y, s);
+    s = fmaf(b.x, w2.x, s); s = fmaf(b.y, w2.y, s); s = fmaf(b.z, w3.x, s); s = fmaf(b.w, w3.y, s);
+    return s;
+}
+__device__ __forceinline__ float row_dot(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int lane) {
+    float s0 = 0.f, s1 = 0.f;
+    if ((n & 7) == 0) {
+        const uint4* w4 = reinterpret_cast<const uint4*>(w);
+        const int n8 = n >> 3;
+        int k = lane;
+        for (; k + 32 < n8; k += 64) {
+            const uint4 v0 = __ldg(w4 + k), v1 = __ldg(w4 + k + 32);
+            s0 = dot8(x + 8 * k, v0, s0);
+            s1 = dot8(x + 8 * (k + 32), v1, s1);
+        }
+        if (k < n8) s0 = dot8(x + 8 * k, __ldg(w4 + k), s0);
+    } else {
+        for (int k = lane; k < n; k += 32) s0 = fmaf(x[k], __bfloat162float(w[k]), s0);
+    }
+    return warp_sum(s0 + s1);
+}
+
 constexpr int MX_WARPS = 8;
 constexpr int MX_PER_WARP = 4;        // output rows a warp makes one after the other
 
@@ -106,7 +139,7 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restri
                                                                const int* __restrict__ ids, T* __restrict__ u, int top, int D,
                                                                int F, int act) {
     pdl_launch_dependents();
-    extern __shared__ float xs[];                 // [D]
+    extern __shared__ __align__(16) float xs[];   // [D]
     const int pair = blockIdx.x, t = pair / top, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     for (int d = tid; d < D; d += MX_WARPS * 32) xs[d] = to_f32(h[(size_t)t * D + d]);
@@ -116,10 +149,7 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restri
     for (int i = 0; i < MX_PER_WARP; ++i) {
         const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
         if (f >= F) break;
-        const T* wr = w + (size_t)f * D;
-        float s = 0.f;
-        for (int d = lane; d < D; d += 32) s = fmaf(xs[d], to_f32(wr[d]), s);
-        s = warp_sum(s);
+        const float s = row_dot(xs, w + (size_t)f * D, D, lane);
         if (lane == 0) u[(size_t)pair * F + f] = from_f32<T>(moe_act(s, act));
     }
 }
@@ -132,7 +162,7 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
                                                                  int zs_stride, float* __restrict__ x, int accumulate, int top,
                                                                  int D, int F) {
     pdl_launch_dependents();
-    extern __shared__ float us[];                 // [top][F]
+    extern __shared__ __align__(16) float us[];   // [top][F]
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     for (int i = tid; i < top * F; i += MX_WARPS * 32) us[i] = to_f32(u[(size_t)t * top * F + i]);
@@ -144,9 +174,7 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
         float y = 0.f;
         for (int j = 0; j < top; ++j) {
             const T* wr = w_down + ((size_t)ids[(size_t)t * top + j] * D + d) * F;
-            float s = 0.f;
-            for (int f = lane; f < F; f += 32) s = fmaf(us[j * F + f], to_f32(wr[f]), s);
-            y = fmaf(weights[(size_t)t * top + j], warp_sum(s), y);
+            y = fmaf(weights[(size_t)t * top + j], row_dot(us + j * F, wr, F, lane), y);
         }
         if (lane == 0) {
             if (shared) y = fmaf(sg, shared[(size_t)t * D + d], y);

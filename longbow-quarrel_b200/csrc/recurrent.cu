@@ -440,12 +440,60 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
     }
 }
 
+// The same for heads of many values (all heads normed together count as one head): a block per (row, head).
+template <typename T>
+__global__ void __launch_bounds__(256) head_norm_gate_wide_kernel(const float* __restrict__ raw, int dvx,
+                                                                  const float* __restrict__ exp_neg_m,
+                                                                  const float* __restrict__ weight, const T* __restrict__ gate,
+                                                                  int gate_stride, int act, T* __restrict__ out, int H, int dv,
+                                                                  float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[8];
+    const int pair = blockIdx.x, tid = threadIdx.x;
+    const int row = pair / H, h = pair % H;
+    const float* r = raw + (size_t)pair * dvx;
+    float inv = 1.f;
+    if (exp_neg_m) inv = 1.f / (fmaxf(fabsf(r[dv]), exp_neg_m[pair]) + 1e-6f);
+    float s = 0.f;
+    for (int d = tid; d < dv; d += 256) {
+        const float v = r[d] * inv;
+        s = fmaf(v, v, s);
+    }
+    s = warp_sum(s);
+    if ((tid & 31) == 0) red[tid >> 5] = s;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += red[w];
+    const float scale = inv / sqrtf(total / (float)dv + eps);
+    for (int d = tid; d < dv; d += 256) {
+        float v = r[d] * scale;
+        if (weight) v *= weight[h * dv + d];
+        if (act) {
+            const float g = to_f32(gate[(size_t)row * gate_stride + h * dv + d]);
+            const float sg = 1.f / (1.f + expf(-g));
+            v *= act == 1 ? sg : g * sg;
+        }
+        out[(size_t)row * H * dv + h * dv + d] = from_f32<T>(v);
+    }
+}
+
 LQ_EXPORT int lq_head_norm_gate(const float* raw, int dvx, const float* exp_neg_m, const float* weight, const void* gate,
                                 int gate_stride, int act, void* out, int dtype, int rows, int H, int dv, float eps,
                                 cudaStream_t stream) {
     const int n = rows * H;
     if (n <= 0) return LQ_OK;
     if (act < 0 || act > 2 || (act && !gate)) return LQ_BAD_SIZE;
+    if (dv >= 512) {
+        if (dtype == LQ_F32)
+            return launch_pdl(head_norm_gate_wide_kernel<float>, dim3(n), dim3(256), 0, stream, raw, dvx, exp_neg_m, weight,
+                              (const float*)gate, gate_stride, act, (float*)out, H, dv, eps);
+        if (dtype == LQ_BF16)
+            return launch_pdl(head_norm_gate_wide_kernel<__nv_bfloat16>, dim3(n), dim3(256), 0, stream, raw, dvx, exp_neg_m, weight,
+                              (const __nv_bfloat16*)gate, gate_stride, act, (__nv_bfloat16*)out, H, dv, eps);
+        return LQ_BAD_DTYPE;
+    }
     dim3 grid((n + 3) / 4);
     if (dtype == LQ_F32)
         return launch_pdl(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, raw, dvx, exp_neg_m, weight,

@@ -555,13 +555,65 @@ def group_rows(ids: torch.Tensor, G: int) -> tuple:
     return rows, group_off, tile_off
 
 
+GROUP_TILE = 128       # rows of a tile of gemm_tc: the padded order gives every group whole tiles
+
+
+def group_rows_padded(ids: torch.Tensor, G: int) -> tuple:
+    """ids int32 [n], each in [0, G) -> (src [cap], dst [n], tile_group [cap / 128]) on the device: the indices group by
+    group with every group padded to whole tiles of 128 places (src: the index at each place, -1 for padding; dst: the
+    place of each index; tile_group: each tile's group, -1 behind the last)."""
+    n = ids.numel()
+    cap = (-(-n // GROUP_TILE) + G) * GROUP_TILE
+    src = torch.empty(cap, dtype=torch.int32, device=ids.device)
+    dst = torch.empty(n, dtype=torch.int32, device=ids.device)
+    tile_group = torch.empty(cap // GROUP_TILE, dtype=torch.int32, device=ids.device)
+    fn = _fn("grouped_gemm", "lq_group_rows_padded", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_p(_contig(ids, "ids")), n, G, GROUP_TILE, cap, _p(src), _p(dst), _p(tile_group), _stream()), "group_rows_padded")
+    return src, dst, tile_group
+
+
+def gather_rows(a: torch.Tensor, src: torch.Tensor, div: int = 1) -> torch.Tensor:
+    """out[p] = a[src[p] // div] (zeros where src[p] < 0); rows of a multiple of 16 bytes."""
+    row_bytes = a.shape[1] * a.element_size()
+    if not a.is_contiguous() or row_bytes % 16:
+        raise KernelError("gather_rows: contiguous rows of a multiple of 16 bytes")
+    out = torch.empty((src.numel(), a.shape[1]), dtype=a.dtype, device=a.device)
+    fn = _fn("grouped_gemm", "lq_gather_rows", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_p(a), _p(src), div, _p(out), src.numel(), row_bytes, _stream()), "gather_rows")
+    return out
+
+
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """a [M, K] (M a multiple of 128, its row tiles each of one group) times w [G, N, K]: row tile i is multiplied with
+    w[tile_group[i]] on the tcgen05 tensor cores (tiles with group -1 are left out and their rows of the result are not
+    written).  Returns [M, N] in out_dtype (bfloat16 or float32)."""
+    M, K = a.shape
+    G, N, K2 = w.shape
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K2 != K or K % 8 or M % GROUP_TILE or not a.is_contiguous() \
+            or not w.is_contiguous() or tile_group.numel() != M // GROUP_TILE:
+        raise KernelError("gemm_tc_grouped: contiguous bfloat16 operands, K a multiple of 8, whole row tiles with a group each")
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    fn = _fn("gemm_tc", "lq_gemm_tc_grouped", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_p(a), _p(w), _p(out), int(out_dtype == torch.float32), M, N, K, G, _p(tile_group), _stream()), "gemm_tc_grouped")
+    return out
+
+
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, accumulate: bool = True,
-                shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
-    """x[t] (+)= sum_j weights[t, j] y[t * top + j] (+ sigmoid(shared_gate[t]) * shared[t]); y float32 [T * top, D]."""
+                shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None,
+                place: torch.Tensor | None = None) -> torch.Tensor:
+    """x[t] (+)= sum_j weights[t, j] y[t * top + j] (+ sigmoid(shared_gate[t]) * shared[t]); y float32 [T * top, D].
+    place int32 [T * top]: the row of y that holds pair t * top + j (y then has any number of rows)."""
     T, top = weights.shape
     D = y.shape[1]
-    if y.dtype != torch.float32 or tuple(y.shape) != (T * top, D) or not y.is_contiguous() or tuple(x.shape) != (T, D):
+    if y.dtype != torch.float32 or not y.is_contiguous() or tuple(x.shape) != (T, D) or (place is None and y.shape[0] != T * top):
         raise KernelError("moe_combine: float32 rows [T * top, D] and [T, D]")
+    if place is not None:
+        fn = _fn("grouped_gemm", "lq_moe_combine_at", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                       c_int, c_int, c_void_p])
+        _check(fn(_p(y), _p(place), _p(_contig(weights, "weights")), _p(shared), _p(shared_gate),
+                  shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), T, top, D, _stream()),
+               "moe_combine")
+        return x
     fn = _fn("grouped_gemm", "lq_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                 c_void_p])
     _check(fn(_p(y), _p(_contig(weights, "weights")), _p(shared), _p(shared_gate),

@@ -120,11 +120,11 @@ class LatentAttention(Mixer):
         H, R = self.H, self.R
         more = {"out_dtype": torch.bfloat16} if self.tc_heads else {}
         if ops.latent_attention_tc_takes(pages, cache_view.page_size):
-            chunks = -(-R // (64 if R <= 64 else 128 if R <= 128 else 256))
+            chunks = -(-R // 512) if R > 256 else 1          # blocks along the value columns (two chunks of 256 share a block)
             if ctx.decode:
                 return ops.latent_attention_tc(wide, pages, cache_view.page_table, ctx.slots, H, R, cache_view.page_size,
                                                self.scale, self.window, tok_pos=ctx.tok_pos, tok_seq=ctx.tok_seq,
-                                               splits=self._splits(ctx, -(-H // 64) * chunks, 2), **more)
+                                               splits=self._splits(ctx, -(-H // 64) * chunks), **more)
             flat = ctx.extra.get(f"latent_blocks{ops.latent_tc_tokens(H)}")
             if flat is not None and flat.numel():
                 return ops.latent_attention_tc(wide, pages, cache_view.page_table, ctx.slots, H, R, cache_view.page_size,

@@ -11,7 +11,9 @@ token behind one sigmoid number per token.  The router's logits and the shared e
 from one 32-bit product; choice and weights are one kernel.  Few tokens (a decode step): the experts' two
 products are one kernel each that streams every token's own experts (`csrc/moe.cu`), the second of which also
 adds the shared expert's rows and joins the stream.  Many tokens (a prompt, bfloat16): the (token, choice) pairs
-are sorted by expert on the device and each product is one grouped tensor-core launch (`csrc/grouped_gemm.cu`).
+are sorted by expert on the device and each product is one grouped tensor-core launch: on tcgen05 for a long
+prompt (`lq_gemm_tc_grouped`: every expert's rows padded to whole tiles), on mma.sync for a short one
+(`csrc/grouped_gemm.cu`).
 Every kernel reads the chosen experts from device memory, so a step can be captured and replayed.
 """
 from __future__ import annotations
@@ -29,6 +31,7 @@ from .spec import PartSpec
 class RoutedExperts(FeedForward):
     graph_safe = True
     GROUPED_FROM = 256       # (token, choice) pairs from which the experts' products run as grouped tensor-core products
+    TILED_FROM = 2048        # ... and from which they run on tcgen05, every expert's rows padded to whole tiles of 128
 
     @property
     def kernel_libraries(self):
@@ -86,6 +89,18 @@ class RoutedExperts(FeedForward):
         shared = self.shared.forward(h, ctx, None) if self.shared is not None else None
         gate = z[:, self.E] if self.shared is not None else None
         T = h.shape[0]
+        if T * self.top >= self.TILED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
+            # A prompt: the pairs in the order of their experts, every expert padded to whole row tiles, so that each
+            # tile of the tcgen05 product reads one expert's weight; the second product reads the first one's rows as
+            # they lie, and the combination finds each pair's row through the order's inverse.
+            src, dst, tile_group = ops.group_rows_padded(ids.view(-1), self.E)
+            u = ops.gemm_tc_grouped(ops.gather_rows(h, src, self.top), self.w_up, tile_group, h.dtype)
+            if self.activation is not None:
+                ops.activation(u, self.activation, out=u)
+            y = ops.gemm_tc_grouped(u, self.w_down, tile_group, torch.float32)
+            out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
+            ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate, place=dst)
+            return None if residual is not None else out
         if T * self.top >= self.GROUPED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
             # Many tokens: the pairs sorted by expert (on the device), each expert's rows as tiles of a tensor-core product.
             listed = ops.group_rows(ids.view(-1), self.E)

@@ -454,3 +454,39 @@ def test_the_experts_products_as_grouped_products(T, E, top, D, F):
     # the streaming kernels make the same rows
     u2 = ops.moe_up(h.to(DEV), w_up.to(DEV), ids.to(DEV), "gelu")
     assert _rel(u2, u.reshape(T, top, F)) < 4e-3
+
+
+@pytest.mark.parametrize("T,E,top,D,F", [(300, 6, 1, 128, 48), (700, 16, 3, 104, 56), (512, 64, 6, 256, 320), (130, 3, 3, 64, 24)])
+def test_the_experts_products_on_tcgen05_in_the_padded_order(T, E, top, D, F):
+    """Every expert's pairs padded to whole tiles of 128 rows, both products as one tcgen05 launch each whose row tiles
+    pick their expert's weight, tiles behind the last left out (their rows stay as they were: NaN here)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + E)
+    h = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    w_up = (torch.randn(E, F, D, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+    w_down = (torch.randn(E, D, F, generator=g) / math.sqrt(F)).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    if top == 1:
+        ids[ids == 1] = 2                                   # an expert that nobody chose
+    weights = torch.rand(T, top, generator=g)
+    src, dst, tile_group = ops.group_rows_padded(ids.to(DEV).view(-1), E)
+    src_h, dst_h, tg = src.cpu().long(), dst.cpu().long(), tile_group.cpu().tolist()
+    flat = ids.view(-1).long()
+    assert (src_h[dst_h] == torch.arange(T * top)).all() and int((src_h >= 0).sum()) == T * top
+    for tile, grp in enumerate(tg):
+        inside = src_h[tile * 128:(tile + 1) * 128]
+        assert (grp == -1 and (inside < 0).all()) or (flat[inside[inside >= 0]] == grp).all()
+    a = ops.gather_rows(h.to(DEV), src, top)
+    assert (a.cpu()[dst_h].double() == h.double()[torch.arange(T * top) // top]).all() and float(a.cpu()[src_h < 0].abs().max()) == 0.0
+    u = ops.gemm_tc_grouped(a, w_up.to(DEV), tile_group, torch.bfloat16)
+    ops.activation(u, "gelu", out=u)
+    pre = torch.einsum("tjfd,td->tjf", w_up.double()[ids.long()], h.double())
+    got_u = u.cpu()[dst_h].reshape(T, top, F)
+    assert _rel(got_u, 0.5 * pre * (1 + torch.erf(pre / math.sqrt(2.0)))) < 6e-3
+    y = ops.gemm_tc_grouped(u, w_down.to(DEV), tile_group, torch.float32)
+    y_ref = torch.einsum("tjdf,tjf->tjd", w_down.double()[ids.long()], got_u.double())
+    assert _rel(y.cpu()[dst_h].reshape(T, top, D), y_ref) < 2e-5
+    x = torch.zeros(T, D, device=DEV)
+    ops.moe_combine(y, weights.to(DEV), x, False, place=dst)
+    assert _rel(x, (weights.double()[:, :, None] * y_ref).sum(1)) < 2e-5
+    ops.check_status()
