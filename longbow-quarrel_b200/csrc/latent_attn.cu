@@ -310,11 +310,11 @@ LQ_EXPORT int lq_latent_attention(const float* q, const void* pages, int cache_d
                                   float* part_ml, int T, int H, int R, int Dk, int page_size, float scale, int window,
                                   int splits, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
-    if (R < 1 || R > Dk || R > 512 || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return LQ_BAD_SIZE;
+    if (R < 1 || R > Dk || R > 1024 || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return LQ_BAD_SIZE;
     typedef __nv_bfloat16 bf;
 #define LQ_GO(TC, NACC) return latent_attention_launch<TC, NACC>(q, pages, page_table, pt_stride, tok_pos, tok_seq, slots, out, \
         part_o, part_ml, T, H, R, Dk, page_size, scale, window, splits, stream)
-#define LQ_BY_R(TC) do { if (R <= 64) LQ_GO(TC, 2); if (R <= 128) LQ_GO(TC, 4); if (R <= 256) LQ_GO(TC, 8); LQ_GO(TC, 16); } while (0)
+#define LQ_BY_R(TC) do { if (R <= 64) LQ_GO(TC, 2); if (R <= 128) LQ_GO(TC, 4); if (R <= 256) LQ_GO(TC, 8); if (R <= 512) LQ_GO(TC, 16); LQ_GO(TC, 32); } while (0)
     if (cache_dtype == LQ_F32) LQ_BY_R(float);
     if (cache_dtype == LQ_BF16) LQ_BY_R(bf);
 #undef LQ_BY_R

@@ -140,8 +140,8 @@ def prepare(dtype: torch.dtype, verbose: bool = True, extra: tuple = ()) -> None
     """Build and load the libraries a model of this dtype uses, before the first step.  extra: libraries
     that parts of the model name beyond the common ones (`Part.kernel_libraries`)."""
     from concurrent.futures import ThreadPoolExecutor
-    names = ["plain_kernels", *extra] + (["gemm_skinny", "gemm_tc", "attn_decode", "attn_prefill", "attn_prefill_tc"]
-                                             if dtype == torch.bfloat16 else [])
+    names = ["plain_kernels", *extra] + (["gemm_skinny", "gemm_tc", "gemm_pair"] if dtype == torch.bfloat16 else [])
+    names = list(dict.fromkeys(names))
     with ThreadPoolExecutor(max_workers=len(names)) as pool:
         list(pool.map(build.build, names))
     for name in names:
@@ -462,8 +462,8 @@ def latent_attention(q: torch.Tensor, pages: torch.Tensor, page_table, tok_pos, 
     T, Hq, Dk = q.shape
     if q.dtype != torch.float32 or not q.is_contiguous() or Hq != H or pages.shape[-1] != Dk or not pages.is_contiguous():
         raise KernelError("latent_attention: contiguous float32 queries [T, H, Dk] and cache rows of Dk numbers")
-    if R > 512:
-        raise KernelError(f"latent_attention: a latent of {R} numbers exceeds 512")
+    if R > 1024:
+        raise KernelError(f"latent_attention: a latent of {R} numbers exceeds 1024")
     out = torch.empty((T, H, R), dtype=torch.float32, device=q.device)
     part_o = part_ml = None
     if splits > 1:

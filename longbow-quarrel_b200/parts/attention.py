@@ -40,6 +40,11 @@ class Attention(Mixer):
     folds_norm = True
     returns_branch = True
 
+    @property
+    def kernel_libraries(self):
+        """The tensor-core attention kernels, built with the model's other libraries before its first step."""
+        return ("attn_decode", "attn_prefill", "attn_prefill_tc") if self.runtime.dtype == torch.bfloat16 else ()
+
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, position: PartSpec | None = None, window: int | None = None,
                  own_kv: bool = True, names: dict | None = None, value_dim: int | None = None, bias: bool = False,

@@ -47,8 +47,8 @@ class LatentAttention(Mixer):
                  window: int | None = None, gate: str | None = None, names: dict | None = None):
         if gate not in (None, "sigmoid"):
             raise ValueError(f"latent_attention: gate {gate!r} is not supported (supported: 'sigmoid')")
-        if kv_rank > 512:
-            raise ValueError(f"latent_attention: a latent of {kv_rank} numbers exceeds 512")
+        if kv_rank > 1024:
+            raise ValueError(f"latent_attention: a latent of {kv_rank} numbers exceeds 1024")
         self.runtime, self.D, self.H = runtime, hidden_size, n_heads
         self.dn, self.dr, self.dv, self.Rq, self.R = head_dim, rot_dim, value_dim, q_rank, kv_rank
         self.scale, self.eps, self.window, self.gate = float(scale), float(eps), window, gate

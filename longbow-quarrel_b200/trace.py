@@ -30,13 +30,16 @@ import sys
 from pathlib import Path
 
 
+PAGE_SLACK = 64
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens that live requests hold at any time (each rounded up to 64)")
+                    help="most tokens that live requests hold at any time (the cache is sized for them plus a page for each of 64 requests)")
     ap.add_argument("--layer-stats", action="store_true",
                     help="also write <step>.layers.f32: RMS of the residual stream of each wanted row after every layer")
     ap.add_argument("--kernel-counts", action="store_true", help="write kernels.json: launches by kernel, at the end")
@@ -52,7 +55,9 @@ def main(argv=None) -> int:
     import torch
     from longbow_quarrel_b200.engine import Engine
 
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
+    # The count leaves out what each request's last page holds beyond its tokens: room for a page more for each of
+    # PAGE_SLACK requests that may be live at a time.
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 64 * PAGE_SLACK)
     layer_rms: list = []
     if args.layer_stats:
         def probe(run, x, ctx):

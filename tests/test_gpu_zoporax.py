@@ -53,7 +53,8 @@ def _check(got: dict, requests: dict, folder, dtype: str, what: str):
 # ------------------------------------------------------------------ each mechanism alone
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["only_latent", "only_latent_full", "only_lightning", "only_dense", "only_moe", "only_moe_plain"])
+@pytest.mark.parametrize("name", ["only_latent", "only_latent_full", "only_latent_ragged", "only_lightning", "only_dense", "only_moe",
+                                  "only_moe_plain"])
 def test_one_layer_of_each_kind_whole_and_token_by_token(tmp_path, name, dtype):
     """A model of one layer: the whole prompt in one step (its first tokens included), and the same tokens one by
     one from the first (133 steps: across two page borders and, for the window of 20, far past it; replayed from a

@@ -490,3 +490,21 @@ def test_the_experts_products_on_tcgen05_in_the_padded_order(T, E, top, D, F):
     ops.moe_combine(y, weights.to(DEV), x, False, place=dst)
     assert _rel(x, (weights.double()[:, :, None] * y_ref).sum(1)) < 2e-5
     ops.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dv", [(1, 600), (2, 512), (1, 2048), (1, 48)])
+def test_all_heads_normed_together_with_weight_and_gate(dtype, H, dv):
+    """The scan's raw outputs over the root mean square of a whole row (all heads as one head, or long heads), times a
+    weight, times the gate's sigmoid: the form for heads of 512 values and more (a block per row) and the narrow one."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(dv)
+    rows = 9
+    raw = 3.0 * torch.randn(rows, H, dv, generator=g)
+    weight = 1 + 0.3 * torch.randn(H * dv, generator=g)
+    gate = torch.randn(rows, H * dv + 7, generator=g).to(dtype)
+    out = ops.head_norm_gate(raw.to(DEV), dv, 1e-5, dtype, weight=weight.to(DEV), gate=gate.to(DEV)[:, 3:3 + H * dv], act="sigmoid")
+    x = raw.double()
+    ref = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * weight.double().reshape(H, dv)
+    ref = ref.reshape(rows, H * dv) * torch.sigmoid(gate.double()[:, 3:3 + H * dv])
+    assert _rel(out, ref) < (2e-6 if dtype == torch.float32 else 4e-3)

@@ -65,7 +65,7 @@ def test_steps_files_and_slots(tmp_path, monkeypatch, capsys):
     assert trace.main(["--model", "DIR", "--dtype", "float32", "--out", str(out), "--max-tokens", "128"]) == 0
     assert capsys.readouterr().out.split("\n")[:4] == ["done 0", "done 1", "done 2", "done 9"]
     eng = ScriptedEngine.made[-1]
-    assert eng.kw == dict(folder="DIR", dtype="float32", max_tokens=128)
+    assert eng.kw == dict(folder="DIR", dtype="float32", max_tokens=128 + 64 * trace.PAGE_SLACK)
     # wanted places in the order of the entries and of want, little-endian float32 [wanted, vocab]
     got = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, ScriptedEngine.VOCAB)
     assert got[:, :3].tolist() == [[0, 0, 0], [0, 0, 2], [1, 0, 0]]

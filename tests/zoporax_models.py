@@ -79,6 +79,9 @@ CONFIGS = {
     "only_latent": model(48, 90, [latent(4, 8, 8, 12, 24, 16, window=20, rot={"dims": 8, "base": 100.0, "scaling": {
         "factor": 2.0, "original": 32, "fast": 8.0, "slow": 1.0}}, scale=0.4)]),
     "only_latent_full": model(48, 90, [latent(2, 16, 4, 8, 16, 36, rot={"dims": 4, "base": 50.0})]),
+    # sizes that no tensor-core kernel takes (cache rows of 26 numbers, heads of 10 + 6): the plain kernels in bfloat16 too
+    "only_latent_ragged": model(44, 90, [latent(3, 10, 6, 14, 20, 20, window=17, rot={"dims": 4, "base": 200.0, "scaling": {
+        "factor": 3.0, "original": 16, "fast": 4.0, "slow": 1.0}}, scale=0.3, mlp=moe(4, 2, 12, groups=(2, 1), shared=20))]),
     "only_lightning": model(48, 90, [lightning(3, 16, 8, [0.7, 0.95, 0.999])]),
     "only_dense": model(40, 70, [lightning(1, 8, 8, [0.9], mlp=dense(56))]),
     "only_moe": model(40, 70, [lightning(1, 8, 8, [0.9], mlp=moe(8, 2, 16, groups=(4, 1), scale=0.5, shared=24))]),
