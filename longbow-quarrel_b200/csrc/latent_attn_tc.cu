@@ -114,12 +114,12 @@ __global__ void __launch_bounds__(NT * NCH, 1) latent_attention_tc_kernel(Latent
     auto load_keys = [&](int tile, int stage) {
         const int kb = tile * BN;
         __nv_bfloat16* sk = sq + BM * LQ + stage * BN * LD;
+        // A tile of 32 keys lies inside one page (pages are multiples of 32 keys long): one look at the page table.
+        const __nv_bfloat16* rows = a.pages + ((size_t)pt[kb / a.page_size] * a.page_size + kb % a.page_size) * Dk;
         for (int i = tid; i < BN * (DKP / 8); i += THREADS) {
-            const int r = i / (DKP / 8), c = (i % (DKP / 8)) * 8, kp = kb + r;
-            const bool ok = kp <= key_last && c < Dk;
-            const __nv_bfloat16* src = a.pages;
-            if (ok) src += ((size_t)pt[kp / a.page_size] * a.page_size + kp % a.page_size) * Dk + c;
-            cp_async16((uint32_t)__cvta_generic_to_shared(sk + r * LD + c), src, ok);
+            const int r = i / (DKP / 8), c = (i % (DKP / 8)) * 8;
+            const bool ok = kb + r <= key_last && c < Dk;
+            cp_async16((uint32_t)__cvta_generic_to_shared(sk + r * LD + c), ok ? rows + (size_t)r * Dk + c : a.pages, ok);
         }
     };
 

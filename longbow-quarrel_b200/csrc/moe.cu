@@ -99,10 +99,11 @@ __device__ __forceinline__ float moe_act(float v, int act) {
 
 // sum_k x[k] * w[k] over a row of n numbers, by one warp (x float32 in shared memory).  bfloat16 rows whose length is a
 // multiple of 8 are read 16 bytes a lane at a time (rows then start on 16-byte boundaries), two loads in flight.
-__device__ __forceinline__ float row_dot(const float* __restrict__ x, const float* __restrict__ w, int n, int lane) {
+// (The lane's share of the sum: the caller adds the lanes with warp_sum, once for all that it has to add.)
+__device__ __forceinline__ float row_part(const float* __restrict__ x, const float* __restrict__ w, int n, int lane) {
     float s = 0.f;
     for (int k = lane; k < n; k += 32) s = fmaf(x[k], w[k], s);
-    return warp_sum(s);
+    return s;
 }
 __device__ __forceinline__ float dot8(const float* x, uint4 v, float s) {
     const float4 a = *reinterpret_cast<const float4*>(x), b = *reinterpret_cast<const float4*>(x + 4);
@@ -112,7 +113,7 @@ __device__ __forceinline__ float dot8(const float* x, uint4 v, float s) {
     s = fmaf(b.x, w2.x, s); s = fmaf(b.y, w2.y, s); s = fmaf(b.z, w3.x, s); s = fmaf(b.w, w3.y, s);
     return s;
 }
-__device__ __forceinline__ float row_dot(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int lane) {
+__device__ __forceinline__ float row_part(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int lane) {
     float s0 = 0.f, s1 = 0.f;
     if ((n & 7) == 0) {
         const uint4* w4 = reinterpret_cast<const uint4*>(w);
@@ -127,7 +128,7 @@ __device__ __forceinline__ float row_dot(const float* __restrict__ x, const __nv
     } else {
         for (int k = lane; k < n; k += 32) s0 = fmaf(x[k], __bfloat162float(w[k]), s0);
     }
-    return warp_sum(s0 + s1);
+    return s0 + s1;
 }
 
 constexpr int MX_WARPS = 8;
@@ -146,11 +147,18 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restri
     const int e = ids[pair];
     __syncthreads();
     const T* w = w_up + (size_t)e * F * D;
+    // The lanes' shares of all the warp's outputs first (their loads are in flight together), then the sums.
+    float part[MX_PER_WARP];
+#pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
         const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
-        if (f >= F) break;
-        const float s = row_dot(xs, w + (size_t)f * D, D, lane);
-        if (lane == 0) u[(size_t)pair * F + f] = from_f32<T>(moe_act(s, act));
+        part[i] = f < F ? row_part(xs, w + (size_t)f * D, D, lane) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < MX_PER_WARP; ++i) {
+        const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
+        const float s = warp_sum(part[i]);
+        if (lane == 0 && f < F) u[(size_t)pair * F + f] = from_f32<T>(moe_act(s, act));
     }
 }
 
@@ -168,14 +176,22 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
     for (int i = tid; i < top * F; i += MX_WARPS * 32) us[i] = to_f32(u[(size_t)t * top * F + i]);
     __syncthreads();
     const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
+    float part[MX_PER_WARP];
+#pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
         const int d = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
-        if (d >= D) break;
-        float y = 0.f;
-        for (int j = 0; j < top; ++j) {
-            const T* wr = w_down + ((size_t)ids[(size_t)t * top + j] * D + d) * F;
-            y = fmaf(weights[(size_t)t * top + j], row_dot(us + j * F, wr, F, lane), y);
-        }
+        part[i] = 0.f;
+        if (d < D)
+            for (int j = 0; j < top; ++j) {          // the choices in their order, weighted inside each lane's share
+                const T* wr = w_down + ((size_t)ids[(size_t)t * top + j] * D + d) * F;
+                part[i] = fmaf(weights[(size_t)t * top + j], row_part(us + j * F, wr, F, lane), part[i]);
+            }
+    }
+#pragma unroll
+    for (int i = 0; i < MX_PER_WARP; ++i) {
+        const int d = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
+        float y = warp_sum(part[i]);
+        if (d >= D) continue;
         if (lane == 0) {
             if (shared) y = fmaf(sg, shared[(size_t)t * D + d], y);
             float* o = x + (size_t)t * D + d;
