@@ -40,6 +40,8 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (the cache is sized for them plus a page for each of 64 requests)")
+    ap.add_argument("--page-slack", type=int, default=PAGE_SLACK,
+                    help="requests for which the cache holds one page beyond --max-tokens (0: the cache is sized exactly)")
     ap.add_argument("--layer-stats", action="store_true",
                     help="also write <step>.layers.f32: RMS of the residual stream of each wanted row after every layer")
     ap.add_argument("--kernel-counts", action="store_true", help="write kernels.json: launches by kernel, at the end")
@@ -55,9 +57,9 @@ def main(argv=None) -> int:
     import torch
     from longbow_quarrel_b200.engine import Engine
 
-    # The count leaves out what each request's last page holds beyond its tokens: room for a page more for each of
-    # PAGE_SLACK requests that may be live at a time.
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 64 * PAGE_SLACK)
+    # A count that leaves out what each request's last page holds beyond its tokens still fits: room for a page more
+    # for each of --page-slack requests that may be live at a time (0: exactly --max-tokens).
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 64 * args.page_slack)
     layer_rms: list = []
     if args.layer_stats:
         def probe(run, x, ctx):

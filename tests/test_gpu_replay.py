@@ -64,8 +64,8 @@ def test_replay_all_cuts_match_plain(tmp_path, name, dtype):
 
 
 def test_max_tokens_sizes_the_cache_exactly(tmp_path):
-    """--max-tokens is the most tokens live requests hold, each rounded up to 64: the trace runs
-    with exactly that, and is refused with one page less."""
+    """--max-tokens is the most tokens live requests hold, each rounded up to 64: without the slack of a page per
+    request that the program adds by default, the trace runs with exactly that, and is refused with one page less."""
     import subprocess
     import sys
 
@@ -78,7 +78,7 @@ def test_max_tokens_sizes_the_cache_exactly(tmp_path):
     tr.add([("b", [7], [0]), ] , end=[])                      # a's pages are back: 128 held
     tr.add([("c", c, [9])], end=["b", "c"])                   # a new request takes freed pages: 128 + 64
     assert tr.max_tokens == 256
-    got = run_trace(folder, "float32", tr, tmp_path / "exact", max_tokens=256)
+    got = run_trace(folder, "float32", tr, tmp_path / "exact", max_tokens=256, options=["--page-slack", "0"])
     ref = plain_logits(folder, a + [5])
     assert rel_err(got[("a", 70)], ref[70]) < TOL["float32"]
     ref = plain_logits(folder, c)
@@ -86,7 +86,7 @@ def test_max_tokens_sizes_the_cache_exactly(tmp_path):
     import json
     text = "".join(json.dumps(s) + "\n" for s in tr.steps)
     proc = subprocess.run([str(TRACE_RUN), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path / "small"),
-                           "--max-tokens", "192"], input=text, capture_output=True, text=True, timeout=300,
+                           "--max-tokens", "192", "--page-slack", "0"], input=text, capture_output=True, text=True, timeout=300,
                           env={**__import__("os").environ, "LQ_PYTHON": sys.executable})
     assert proc.returncode != 0 and "cache is full" in proc.stderr
     assert proc.stdout.splitlines() == ["done 0"]             # the first step fits; the second does not
